@@ -1,0 +1,117 @@
+/*
+ * wmma_ops_b200 — C ABI of the B200 (sm_100a) GEMM hot path.
+ *
+ * This is the boundary a binding of the reference's PyTorch extension module would call
+ * instead of launching its HIP kernels: plain device pointers and sizes, a CUDA stream
+ * passed as void*, int return codes. No torch types, no exceptions, and — except where a
+ * function says otherwise — no allocation: every buffer, including scratch, is the caller's.
+ *
+ * Conventions
+ *   - all matrix pointers are device pointers, row-major, contiguous, 16-byte aligned;
+ *   - A is [M,K] fp16, B is [K,N] fp16, C is [M,N] fp32 (the reference's layouts,
+ *     wmma_gemm.hip:45-60);
+ *   - every function returns WMMA_OPS_OK (0) or a WMMA_OPS_ERR_* code; the message for the
+ *     last failure on the calling thread is wmma_ops_last_error();
+ *   - launches are asynchronous on `stream` (NULL = the legacy default stream);
+ *   - `status` is an optional device pointer to 4 ints, zeroed by the caller. A kernel
+ *     whose bounded wait gives up writes {code, role, block, detail} there and returns
+ *     early instead of hanging; 0 in status[0] after synchronising means no kernel gave up.
+ */
+#ifndef WMMA_OPS_B200_H
+#define WMMA_OPS_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define WMMA_OPS_OK 0
+#define WMMA_OPS_ERR_INVALID 1     /* bad pointer, shape, alignment or option */
+#define WMMA_OPS_ERR_CUDA 2        /* a CUDA runtime / driver call failed      */
+#define WMMA_OPS_ERR_UNSUPPORTED 3 /* device is not sm_100                     */
+#define WMMA_OPS_ERR_WORKSPACE 4   /* scratch buffer missing or too small      */
+
+/* CTA tile shapes of the tcgen05 GEMM. They take the place of the reference's
+ * TileConfig enum (wmma_tile_selection.hpp:17-23) and of matmul_tiled's 0..3
+ * (wmma_gemm.hip:1504-1523). */
+#define WMMA_OPS_TILE_AUTO (-1)
+#define WMMA_OPS_TILE_128x64 0
+#define WMMA_OPS_TILE_128x128 1
+#define WMMA_OPS_TILE_128x256 2
+#define WMMA_OPS_TILE_256x256_PAIR 3 /* two CTAs (one cluster) share one 256x256 tile */
+
+/* Message of the last failing call on this thread ("" if none). Never NULL. */
+const char* wmma_ops_last_error(void);
+
+/* Library version: major * 10000 + minor * 100 + patch. */
+int wmma_ops_version(void);
+
+/* Tile shape and split-K factor for an M x N x K product on a device with num_sms SMs
+ * (num_sms <= 0: 148). Replaces select_optimal_tile (wmma_tile_selection.hpp:30-66) and
+ * split_k::compute_config (wmma_xor_swizzle.hpp:293-332). Pure host arithmetic. */
+int wmma_ops_select_tile(int M, int N, int K, int num_sms, int* tile_cfg, int* split_k);
+
+/* Bytes of scratch wmma_ops_gemm_f16f32 needs for this split_k (0 when split_k <= 1):
+ * split_k fp32 partial products of M x N, the layout of the reference's split-K
+ * workspace (wmma_xor_swizzle.hpp:1196-1210). */
+size_t wmma_ops_gemm_workspace_bytes(int M, int N, int K, int split_k);
+
+/* C_out = alpha * (A . B) + beta * C_in, fp16 inputs, fp32 accumulate and output.
+ * Replaces the launches in wmma_matmul (wmma_gemm.hip:1432-1470), wmma_matmul_tiled
+ * (:1473-1528), wmma_matmul_adaptive (:1197-1263), wmma_gemm / _inplace / _adaptive
+ * (:1891-2078) and the unbound split-K path (wmma_xor_swizzle.hpp:1172-1219).
+ *   C_in   read only when beta != 0 and C_in != NULL (wmma_gemm.hip:653-660); may equal C_out.
+ *   tile_cfg  WMMA_OPS_TILE_* ; AUTO picks tile and split_k with wmma_ops_select_tile.
+ *   split_k   <= 1: one pass. > 1: K is cut into split_k slices, partials go to
+ *             `workspace` ([split_k][M][N] fp32) and are summed in ascending slice order.
+ *             With tile_cfg AUTO, pass split_k = 0 to let the table decide (the workspace
+ *             must then hold wmma_ops_gemm_workspace_bytes(M, N, K, chosen split_k)).
+ * Requirements: M >= 1, N % 8 == 0, K % 8 == 0 (16-byte row pitch for TMA). */
+int wmma_ops_gemm_f16f32(const void* A, const void* B, const void* C_in, void* C_out, int M, int N,
+                         int K, float alpha, float beta, int tile_cfg, int split_k, void* workspace,
+                         size_t workspace_bytes, int* status, void* stream);
+
+/* INT4 weight prepack ("W4-B200-v1"; the reference snapshot has no INT4 code, so the
+ * format is defined here and restated in oracle/int4.py):
+ *   codes    [K,N] uint8, values 0..15 (weight k,n = (code - 8) * scale[k / group][n])
+ *   qweight  [N, K/8] uint32. Word (n, j) holds k = 8j .. 8j+7 of column n; nibble p
+ *            (bits 4p..4p+3) holds k = 8j + {0,2,4,6,1,3,5,7}[p].
+ * Requirements: K % 64 == 0, N % 8 == 0. */
+int wmma_ops_int4_prepack(const void* codes_u8, void* qweight, int K, int N, void* stream);
+
+/* Inverse of wmma_ops_int4_prepack: qweight -> codes [K,N] uint8. */
+int wmma_ops_int4_unpack(const void* qweight, void* codes_u8, int K, int N, void* stream);
+
+/* W[k][n] = fp16(code - 8) * scales[k / group_size][n] (one fp16 multiply, round to nearest
+ * even), written as [K,N] fp16. scales is [K/group_size, N] fp16. */
+int wmma_ops_int4_dequant(const void* qweight, const void* scales, void* W_f16, int K, int N,
+                          int group_size, void* stream);
+
+/* Bytes of scratch wmma_ops_w4a16_gemm needs (split-K partials + arrival counters). */
+size_t wmma_ops_w4a16_workspace_bytes(int M, int N, int K, int split_k);
+
+/* Split-K factor wmma_ops_w4a16_gemm picks when split_k == 0. */
+int wmma_ops_w4a16_select_split(int M, int N, int K, int num_sms);
+
+/* C[M,N] fp32 = A[M,K] fp16 . W, W dequantised on the fly from qweight / scales inside the
+ * kernel (shared memory), never materialised in global memory.
+ * Requirements: K % 64 == 0, K % group_size == 0, group_size % 64 == 0, N % 8 == 0.
+ * split_k: 0 = auto, 1 = none, > 1 needs workspace (zeroed counters are maintained by the
+ * kernel itself after the first call; pass a buffer that was zero-filled once). */
+int wmma_ops_w4a16_gemm(const void* A, const void* qweight, const void* scales, void* C, int M,
+                        int N, int K, int group_size, int split_k, void* workspace,
+                        size_t workspace_bytes, int* status, void* stream);
+
+/* Flash-attention forward: O = softmax(scale * Q K^T [+ causal mask]) V per (b,h).
+ * Q, K, V, O are [B,H,S,D] fp16 contiguous; the signature documented in the reference's
+ * README.md:221-251 (its implementation is not in the reference tree).
+ * scale < 0 means 1/sqrt(D). Requirements: D == 128 or D == 64, S >= 1. */
+int wmma_ops_fmha_fwd(const void* Q, const void* K, const void* V, void* O, int B, int H, int S,
+                      int D, float scale, int causal, int* status, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* WMMA_OPS_B200_H */

@@ -1,0 +1,34 @@
+"""wmma_ops_b200 — the GEMM hot path of wmma_ops, written for B200 (sm_100a).
+
+Same function names and argument meaning as the reference's extension module
+(wmma_gemm.hip:2120-2156) plus the flash-attention signature its README documents
+(README.md:221-251) and the INT4 prepack / W4A16 pair. Every function runs hand-written
+CUDA through libwmma_ops_b200.so; there is no CPU or library fallback.
+"""
+from . import _lib
+from .ops import (  # noqa: F401
+    check_status,
+    gemm,
+    gemm_adaptive,
+    gemm_inplace,
+    matmul,
+    matmul_adaptive,
+    matmul_asmOpt,
+    matmul_coop,
+    matmul_highOcc,
+    matmul_hilbert,
+    matmul_kunroll,
+    matmul_native,
+    matmul_noPrefetch,
+    matmul_opt,
+    matmul_pingpong,
+    matmul_quad,
+    matmul_splitk,
+    matmul_swizzled,
+    matmul_tiled,
+    matmul_xor_optimized,
+    matmul_zerocopy,
+    select_tile,
+)
+
+__version__ = "0.1.0"

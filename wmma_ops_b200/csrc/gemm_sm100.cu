@@ -1,0 +1,494 @@
+// FP16 x FP16 -> FP32 GEMM for sm_100a: persistent, warp-specialised, tcgen05 MMA with
+// TMEM accumulators, TMA-fed shared-memory ring, fused alpha/beta epilogue, split-K.
+//
+// One kernel family takes the place of the reference's GEMM kernels
+// (wmma_gemm.hip:45-233 main kernel, :475-667 alpha/beta kernel, :697-877 adaptive kernel,
+// wmma_kernel_variants.hpp:28-193 K-unrolled kernel, wmma_kernel_largetile.hpp:169-293,
+// wmma_kernels_pingpong.hpp:25-211, wmma_xor_swizzle.hpp:690-844 split-K kernel and
+// :334-353 reduce kernel).
+//
+// Layouts (the reference's): A [M,K] fp16 row-major, B [K,N] fp16 row-major, C [M,N] fp32.
+//   A tiles are K-major operands (128 rows x 64 halves = 128-byte rows, SWIZZLE_128B).
+//   B tiles are MN-major operands: each TMA box is 64 K-rows x 64 N-halves, so the
+//   reference's global->LDS transpose of B (wmma_device_helpers.hpp:90-172) has no
+//   counterpart here; the MMA reads B with N contiguous.
+//
+// Warp roles per CTA (192 threads): warp 0 = TMA producer, warp 1 = TMEM owner + MMA issuer,
+// warps 2..5 = epilogue (TMEM -> registers -> alpha*acc + beta*C_in -> global).
+// Two TMEM accumulators let the epilogue of one tile overlap the main loop of the next.
+#include "host_common.cuh"
+#include "ptx.cuh"
+
+namespace wb {
+
+constexpr int BM = 128;
+constexpr int BK = 64;
+constexpr int GEMM_THREADS = 192;
+constexpr int RASTER_GROUP_M = 16;  // m-blocks walked together so a wave reuses A and B in L2
+
+template <int BN>
+struct GemmCfg {
+    static constexpr int A_BYTES = BM * BK * 2;
+    static constexpr int B_BOX_BYTES = BK * 64 * 2;  // one 64(k) x 64(n) box
+    static constexpr int B_BYTES = (BN / 64) * B_BOX_BYTES;
+    static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
+    static constexpr int STAGES = (BN == 256) ? 4 : (BN == 128) ? 6 : 8;
+    static constexpr int TMEM_COLS = 2 * BN;
+    static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 /*align*/ + 256 /*barriers*/;
+};
+
+struct GemmParams {
+    const float* C_in;  // may alias C_out, may be null
+    float* C_out;       // [M,N] or, with split_k > 1, the partials [split_k][M][N]
+    int M, N, K;
+    int m_blocks, n_blocks;
+    int split_k;        // >= 1
+    int kb_total;       // ceil(K / 64)
+    int kb_per_split;   // k-blocks per slice
+    float alpha, beta;
+    int* status;        // optional device status word
+};
+
+__device__ __forceinline__ void report_timeout(int* status, int role, int detail) {
+    if (status != nullptr && atomicCAS(status, 0, 1) == 0) {
+        status[1] = role;
+        status[2] = static_cast<int>(blockIdx.x);
+        status[3] = detail;
+    }
+}
+
+// Work unit -> (m block, n block, k slice). Tiles are walked in groups of RASTER_GROUP_M
+// m-blocks, m fastest, which plays the role of the reference's tile rasterisation
+// (wmma_xor_swizzle.hpp:171-278, wmma_tile_mapping.hpp:35-434).
+__device__ __forceinline__ void decode_unit(const GemmParams& p, int unit, int& mb, int& nb,
+                                            int& ks) {
+    const int tiles = p.m_blocks * p.n_blocks;
+    ks = unit / tiles;
+    const int t = unit - ks * tiles;
+    const int group_span = RASTER_GROUP_M * p.n_blocks;
+    const int g = t / group_span;
+    const int first_m = g * RASTER_GROUP_M;
+    const int rows = min(RASTER_GROUP_M, p.m_blocks - first_m);
+    const int r = t - g * group_span;
+    mb = first_m + r % rows;
+    nb = r / rows;
+}
+
+template <int BN>
+__global__ void __launch_bounds__(GEMM_THREADS, 1)
+gemm_f16f32_kernel(const __grid_constant__ CUtensorMap tmap_a,
+                   const __grid_constant__ CUtensorMap tmap_b, const GemmParams p) {
+    using Cfg = GemmCfg<BN>;
+    extern __shared__ uint8_t smem_raw[];
+    const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+    const uint32_t bar_base = smem_base + Cfg::STAGES * Cfg::STAGE_BYTES;
+    // barrier slots (8 bytes each): full[STAGES], empty[STAGES], acc_full[2], acc_empty[2], tmem ptr
+    auto full_bar = [&](int s) { return bar_base + 8u * s; };
+    auto empty_bar = [&](int s) { return bar_base + 8u * (Cfg::STAGES + s); };
+    auto acc_full_bar = [&](int b) { return bar_base + 8u * (2 * Cfg::STAGES + b); };
+    auto acc_empty_bar = [&](int b) { return bar_base + 8u * (2 * Cfg::STAGES + 2 + b); };
+    const uint32_t tmem_slot = bar_base + 8u * (2 * Cfg::STAGES + 4);
+
+    const int warp = threadIdx.x >> 5;
+    const int lane = threadIdx.x & 31;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < Cfg::STAGES; ++s) {
+            mbar_init(full_bar(s), 1);
+            mbar_init(empty_bar(s), 1);
+        }
+        for (int b = 0; b < 2; ++b) {
+            mbar_init(acc_full_bar(b), 1);
+            mbar_init(acc_empty_bar(b), 128);
+        }
+        fence_barrier_init();
+        fence_proxy_async_smem();
+        prefetch_tmap(&tmap_a);
+        prefetch_tmap(&tmap_b);
+    }
+    if (warp == 1) {
+        tmem_alloc(tmem_slot, Cfg::TMEM_COLS);
+        tmem_relinquish();
+    }
+    tc_fence_before_sync();
+    __syncthreads();
+    tc_fence_after_sync();
+    uint32_t tmem_base;
+    asm volatile("ld.shared.u32 %0, [%1];" : "=r"(tmem_base) : "r"(tmem_slot));
+
+    const int total_units = p.m_blocks * p.n_blocks * p.split_k;
+
+    if (warp == 0) {
+        // ------------------------------------------------------------ TMA producer
+        if (lane == 0) {
+            int stage = 0;
+            uint32_t phase = 0;
+            bool ok = true;
+            for (int unit = blockIdx.x; ok && unit < total_units; unit += gridDim.x) {
+                int mb, nb, ks;
+                decode_unit(p, unit, mb, nb, ks);
+                const int kb0 = ks * p.kb_per_split;
+                const int kb1 = min(p.kb_total, kb0 + p.kb_per_split);
+                for (int kb = kb0; kb < kb1; ++kb) {
+                    if (!mbar_wait(empty_bar(stage), phase ^ 1u)) {
+                        report_timeout(p.status, 0, kb);
+                        ok = false;
+                        break;
+                    }
+                    const uint32_t a_dst = smem_base + stage * Cfg::STAGE_BYTES;
+                    const uint32_t b_dst = a_dst + Cfg::A_BYTES;
+                    mbar_arrive_expect_tx(full_bar(stage), Cfg::STAGE_BYTES);
+                    tma_load_2d(a_dst, &tmap_a, full_bar(stage), kb * BK, mb * BM);
+#pragma unroll
+                    for (int j = 0; j < BN / 64; ++j)
+                        tma_load_2d(b_dst + j * Cfg::B_BOX_BYTES, &tmap_b, full_bar(stage),
+                                    nb * BN + j * 64, kb * BK);
+                    if (++stage == Cfg::STAGES) {
+                        stage = 0;
+                        phase ^= 1u;
+                    }
+                }
+            }
+        }
+    } else if (warp == 1) {
+        // ------------------------------------------------------------ MMA issuer
+        if (lane == 0) {
+            constexpr uint32_t idesc = make_idesc_f16_f32(BM, BN, /*a_mn=*/false, /*b_mn=*/true);
+            int stage = 0;
+            uint32_t phase = 0;
+            int acc = 0;
+            uint32_t acc_phase = 0;
+            bool ok = true;
+            for (int unit = blockIdx.x; ok && unit < total_units; unit += gridDim.x) {
+                int mb, nb, ks;
+                decode_unit(p, unit, mb, nb, ks);
+                const int kb0 = ks * p.kb_per_split;
+                const int kb1 = min(p.kb_total, kb0 + p.kb_per_split);
+                if (!mbar_wait(acc_empty_bar(acc), acc_phase ^ 1u)) {
+                    report_timeout(p.status, 1, -1);
+                    break;
+                }
+                tc_fence_after_sync();
+                const uint32_t d_tmem = tmem_base + acc * BN;
+                for (int kb = kb0; kb < kb1; ++kb) {
+                    if (!mbar_wait(full_bar(stage), phase)) {
+                        report_timeout(p.status, 1, kb);
+                        ok = false;
+                        break;
+                    }
+                    tc_fence_after_sync();
+                    const uint32_t a_src = smem_base + stage * Cfg::STAGE_BYTES;
+                    const uint32_t b_src = a_src + Cfg::A_BYTES;
+#pragma unroll
+                    for (int kk = 0; kk < BK / 16; ++kk) {
+                        // A: 16 halves = 32 bytes further along the 128-byte swizzled row.
+                        const uint64_t a_desc = make_smem_desc_sw128(a_src + kk * 32, 16, 1024);
+                        // B: 16 K-rows = two 8-row swizzle atoms = 2048 bytes further.
+                        const uint64_t b_desc =
+                            make_smem_desc_sw128(b_src + kk * 2048, Cfg::B_BOX_BYTES, 1024);
+                        umma_f16(d_tmem, a_desc, b_desc, idesc, (kb > kb0 || kk > 0) ? 1u : 0u);
+                    }
+                    umma_commit(empty_bar(stage));  // frees the smem stage when the MMAs finish
+                    if (++stage == Cfg::STAGES) {
+                        stage = 0;
+                        phase ^= 1u;
+                    }
+                }
+                if (!ok) break;
+                umma_commit(acc_full_bar(acc));  // accumulator complete -> epilogue
+                acc ^= 1;
+                if (acc == 0) acc_phase ^= 1u;
+            }
+        }
+    } else {
+        // ------------------------------------------------------------ epilogue (warps 2..5)
+        const int quad = warp & 3;  // TMEM lane quadrant this warp may read
+        const int row_in_tile = quad * 32 + lane;
+        int acc = 0;
+        uint32_t acc_phase = 0;
+        const bool use_cin = (p.beta != 0.0f) && (p.C_in != nullptr) && (p.split_k == 1);
+        const float alpha = (p.split_k == 1) ? p.alpha : 1.0f;
+        const float beta = p.beta;
+        for (int unit = blockIdx.x; unit < total_units; unit += gridDim.x) {
+            int mb, nb, ks;
+            decode_unit(p, unit, mb, nb, ks);
+            if (!mbar_wait(acc_full_bar(acc), acc_phase)) {
+                report_timeout(p.status, 2, unit);
+                break;
+            }
+            tc_fence_after_sync();
+            const int row = mb * BM + row_in_tile;
+            const size_t slice_off = static_cast<size_t>(ks) * p.M * p.N;
+            float* out_row = p.C_out + slice_off + static_cast<size_t>(row) * p.N;
+            const float* in_row = use_cin ? p.C_in + static_cast<size_t>(row) * p.N : nullptr;
+            const uint32_t t_addr = tmem_base + acc * BN + (static_cast<uint32_t>(quad * 32) << 16);
+#pragma unroll 1
+            for (int c = 0; c < BN / 32; ++c) {
+                uint32_t r[32];
+                tmem_ld_32x32b_x32(t_addr + c * 32, r);
+                tmem_wait_ld();
+                if (row < p.M) {
+                    const int col0 = nb * BN + c * 32;
+#pragma unroll
+                    for (int j = 0; j < 8; ++j) {
+                        const int col = col0 + j * 4;
+                        if (col < p.N) {
+                            float4 v;
+                            v.x = alpha * __uint_as_float(r[4 * j + 0]);
+                            v.y = alpha * __uint_as_float(r[4 * j + 1]);
+                            v.z = alpha * __uint_as_float(r[4 * j + 2]);
+                            v.w = alpha * __uint_as_float(r[4 * j + 3]);
+                            if (use_cin) {
+                                const float4 cin = *reinterpret_cast<const float4*>(in_row + col);
+                                v.x += beta * cin.x;
+                                v.y += beta * cin.y;
+                                v.z += beta * cin.z;
+                                v.w += beta * cin.w;
+                            }
+                            *reinterpret_cast<float4*>(out_row + col) = v;
+                        }
+                    }
+                }
+            }
+            tc_fence_before_sync();
+            mbar_arrive(acc_empty_bar(acc));
+            acc ^= 1;
+            if (acc == 0) acc_phase ^= 1u;
+        }
+    }
+
+    tc_fence_before_sync();
+    __syncthreads();
+    if (warp == 1) {
+        tc_fence_after_sync();
+        tmem_dealloc(tmem_base, Cfg::TMEM_COLS);
+    }
+}
+
+// out[i] = alpha * sum_{s ascending} partial[s][i] + beta * c_in[i]; the order of the
+// reference's reduce kernel (wmma_xor_swizzle.hpp:334-353). With split == 0 it writes
+// beta * c_in (the K == 0 product).
+__global__ void __launch_bounds__(256)
+splitk_reduce_kernel(float* out, const float* __restrict__ partials, const float* c_in,
+                     size_t total4, int split, float alpha, float beta) {
+    const size_t stride = static_cast<size_t>(gridDim.x) * blockDim.x;
+    const bool use_cin = (beta != 0.0f) && (c_in != nullptr);
+    for (size_t i = static_cast<size_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < total4;
+         i += stride) {
+        float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+        for (int s = 0; s < split; ++s) {
+            const float4 v = __ldcs(reinterpret_cast<const float4*>(partials) + s * total4 + i);
+            acc.x += v.x;
+            acc.y += v.y;
+            acc.z += v.z;
+            acc.w += v.w;
+        }
+        acc.x *= alpha;
+        acc.y *= alpha;
+        acc.z *= alpha;
+        acc.w *= alpha;
+        if (use_cin) {
+            const float4 c = reinterpret_cast<const float4*>(c_in)[i];
+            acc.x += beta * c.x;
+            acc.y += beta * c.y;
+            acc.z += beta * c.z;
+            acc.w += beta * c.w;
+        }
+        reinterpret_cast<float4*>(out)[i] = acc;
+    }
+}
+
+// ---------------------------------------------------------------------------- host side
+
+static int ceil_div(int a, int b) { return (a + b - 1) / b; }
+
+static int tile_bn(int tile_cfg) {
+    switch (tile_cfg) {
+        case WMMA_OPS_TILE_128x64: return 64;
+        case WMMA_OPS_TILE_128x128: return 128;
+        case WMMA_OPS_TILE_128x256: return 256;
+        case WMMA_OPS_TILE_256x256_PAIR: return 256;
+        default: return -1;
+    }
+}
+
+// Cost model (clocks per 64-deep k-block of one CTA tile): the MMA needs 2*BN clocks
+// (four 128xBNx16 instructions at 8192 dense fp16 flop/clk/SM), shared memory must
+// deliver the A and B stage (16 KB + BN*128 B) at 128 B/clk; the slower one bounds it.
+static double kblock_cost(int bn) {
+    const double mma = 2.0 * bn;
+    const double smem = 128.0 + bn;
+    return mma > smem ? mma : smem;
+}
+
+static void select_tile_impl(int M, int N, int K, int sms, int* tile_cfg, int* split_k) {
+    const int kb_total = ceil_div(K, BK);
+    const int cfgs[3] = {WMMA_OPS_TILE_128x256, WMMA_OPS_TILE_128x128, WMMA_OPS_TILE_128x64};
+    double best_time = 0.0;
+    int best_cfg = WMMA_OPS_TILE_128x128, best_split = 1;
+    for (int i = 0; i < 3; ++i) {
+        const int bn = tile_bn(cfgs[i]);
+        const int tiles = ceil_div(M, BM) * ceil_div(N, bn);
+        int split = 1;
+        // Split K when the output tiles cannot occupy half the SMs. Like the reference's
+        // plan (wmma_xor_swizzle.hpp:293-332) a slice keeps at least 256 of K and there are
+        // at most 32 slices; unlike it the factor is sized to 148 SMs and need not be a
+        // power of two.
+        if (tiles * 2 <= sms && kb_total >= 8) {
+            split = sms / tiles;
+            if (split > 32) split = 32;
+            if (split > kb_total / 4) split = kb_total / 4;
+            if (split < 1) split = 1;
+            const int per = ceil_div(kb_total, split);
+            split = ceil_div(kb_total, per);
+        }
+        const int units = tiles * split;
+        const int waves = ceil_div(units, sms);
+        const int kb_per = ceil_div(kb_total, split);
+        // fixed per-unit cost: pipeline fill + epilogue drain, in clocks
+        const double unit_cost = kblock_cost(bn) * kb_per + 600.0 + 2.0 * bn;
+        double t = waves * unit_cost;
+        if (split > 1) t += 0.02 * split * (static_cast<double>(M) * N / sms);  // reduce pass
+        if (i == 0 || t < best_time) {
+            best_time = t;
+            best_cfg = cfgs[i];
+            best_split = split;
+        }
+    }
+    *tile_cfg = best_cfg;
+    *split_k = best_split;
+}
+
+template <int BN>
+static int launch_gemm(const CUtensorMap& ta, const CUtensorMap& tb, const GemmParams& p, int sms,
+                       cudaStream_t stream) {
+    using Cfg = GemmCfg<BN>;
+    static bool attr_set[64] = {};
+    int dev = 0;
+    WB_CHECK_CUDA(cudaGetDevice(&dev));
+    if (dev >= 0 && dev < 64 && !attr_set[dev]) {
+        WB_CHECK_CUDA(cudaFuncSetAttribute(gemm_f16f32_kernel<BN>,
+                                           cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                           Cfg::SMEM_BYTES));
+        attr_set[dev] = true;
+    }
+    const int units = p.m_blocks * p.n_blocks * p.split_k;
+    const int grid = units < sms ? units : sms;
+    gemm_f16f32_kernel<BN><<<grid, GEMM_THREADS, Cfg::SMEM_BYTES, stream>>>(ta, tb, p);
+    WB_CHECK_CUDA(cudaGetLastError());
+    return WMMA_OPS_OK;
+}
+
+}  // namespace wb
+
+extern "C" int wmma_ops_select_tile(int M, int N, int K, int num_sms, int* tile_cfg, int* split_k) {
+    WB_REQUIRE(M >= 1 && N >= 1 && K >= 1, WMMA_OPS_ERR_INVALID,
+               "select_tile: M, N, K must be positive (got %d, %d, %d)", M, N, K);
+    WB_REQUIRE(tile_cfg != nullptr && split_k != nullptr, WMMA_OPS_ERR_INVALID,
+               "select_tile: null output pointer");
+    wb::select_tile_impl(M, N, K, num_sms > 0 ? num_sms : 148, tile_cfg, split_k);
+    return WMMA_OPS_OK;
+}
+
+extern "C" size_t wmma_ops_gemm_workspace_bytes(int M, int N, int K, int split_k) {
+    (void)K;
+    if (split_k <= 1 || M <= 0 || N <= 0) return 0;
+    return static_cast<size_t>(split_k) * static_cast<size_t>(M) * static_cast<size_t>(N) *
+           sizeof(float);
+}
+
+extern "C" int wmma_ops_gemm_f16f32(const void* A, const void* B, const void* C_in, void* C_out,
+                                    int M, int N, int K, float alpha, float beta, int tile_cfg,
+                                    int split_k, void* workspace, size_t workspace_bytes,
+                                    int* status, void* stream_) {
+    using namespace wb;
+    cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+    WB_REQUIRE(M >= 0 && N >= 0 && K >= 0, WMMA_OPS_ERR_INVALID,
+               "gemm: negative dimension (M=%d, N=%d, K=%d)", M, N, K);
+    if (M == 0 || N == 0) return WMMA_OPS_OK;
+    WB_REQUIRE(C_out != nullptr, WMMA_OPS_ERR_INVALID, "gemm: C_out is null");
+    WB_REQUIRE(N % 8 == 0, WMMA_OPS_ERR_INVALID,
+               "N must be a multiple of 8 for 16-byte row pitch (got N=%d)", N);
+    WB_REQUIRE(K % 8 == 0, WMMA_OPS_ERR_INVALID,
+               "K must be a multiple of 8 for 16-byte row pitch (got K=%d)", K);
+    WB_REQUIRE((reinterpret_cast<uintptr_t>(C_out) % 16) == 0, WMMA_OPS_ERR_INVALID,
+               "C must be 16-byte aligned");
+    WB_REQUIRE(C_in == nullptr || (reinterpret_cast<uintptr_t>(C_in) % 16) == 0,
+               WMMA_OPS_ERR_INVALID, "C must be 16-byte aligned");
+
+    const size_t total4 = static_cast<size_t>(M) * N / 4;
+    const int sms = sm_count();
+    auto launch_reduce = [&](const float* partials, int split) -> int {
+        size_t blocks = (total4 + 255) / 256;
+        const size_t cap = static_cast<size_t>(sms) * 8;
+        if (blocks > cap) blocks = cap;
+        splitk_reduce_kernel<<<static_cast<unsigned>(blocks), 256, 0, stream>>>(
+            static_cast<float*>(C_out), partials, static_cast<const float*>(C_in), total4, split,
+            alpha, beta);
+        WB_CHECK_CUDA(cudaGetLastError());
+        return WMMA_OPS_OK;
+    };
+    if (K == 0) return launch_reduce(nullptr, 0);
+
+    WB_REQUIRE(A != nullptr && B != nullptr, WMMA_OPS_ERR_INVALID, "gemm: A or B is null");
+    WB_REQUIRE((reinterpret_cast<uintptr_t>(A) % 16) == 0, WMMA_OPS_ERR_INVALID,
+               "A must be 16-byte aligned");
+    WB_REQUIRE((reinterpret_cast<uintptr_t>(B) % 16) == 0, WMMA_OPS_ERR_INVALID,
+               "B must be 16-byte aligned");
+
+    if (tile_cfg == WMMA_OPS_TILE_AUTO) {
+        int auto_split = 1;
+        select_tile_impl(M, N, K, sms, &tile_cfg, &auto_split);
+        if (split_k == 0) split_k = auto_split;
+    }
+    const int bn = tile_bn(tile_cfg);
+    WB_REQUIRE(bn > 0, WMMA_OPS_ERR_INVALID,
+               "Invalid tile_config: 0=128x64, 1=128x128, 2=128x256, 3=256x256 (CTA pair)");
+    if (split_k < 1) split_k = 1;
+
+    GemmParams p;
+    p.M = M;
+    p.N = N;
+    p.K = K;
+    p.m_blocks = ceil_div(M, BM);
+    p.n_blocks = ceil_div(N, bn);
+    p.kb_total = ceil_div(K, BK);
+    if (split_k > p.kb_total) split_k = p.kb_total;
+    p.kb_per_split = ceil_div(p.kb_total, split_k);
+    split_k = ceil_div(p.kb_total, p.kb_per_split);  // no empty slice
+    p.split_k = split_k;
+    p.alpha = alpha;
+    p.beta = beta;
+    p.status = status;
+    p.C_in = static_cast<const float*>(C_in);
+    if (split_k > 1) {
+        const size_t need = wmma_ops_gemm_workspace_bytes(M, N, K, split_k);
+        WB_REQUIRE(workspace != nullptr && workspace_bytes >= need, WMMA_OPS_ERR_WORKSPACE,
+                   "gemm: split_k=%d needs %zu bytes of workspace (got %zu)", split_k, need,
+                   workspace_bytes);
+        WB_REQUIRE((reinterpret_cast<uintptr_t>(workspace) % 16) == 0, WMMA_OPS_ERR_INVALID,
+                   "workspace must be 16-byte aligned");
+        p.C_out = static_cast<float*>(workspace);
+    } else {
+        p.C_out = static_cast<float*>(C_out);
+    }
+
+    CUtensorMap ta, tb;
+    int rc = encode_tmap_2d(&ta, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, A, static_cast<uint64_t>(K),
+                            static_cast<uint64_t>(M), static_cast<uint64_t>(K) * 2, BK, BM,
+                            CU_TENSOR_MAP_SWIZZLE_128B);
+    if (rc != WMMA_OPS_OK) return rc;
+    rc = encode_tmap_2d(&tb, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, B, static_cast<uint64_t>(N),
+                        static_cast<uint64_t>(K), static_cast<uint64_t>(N) * 2, 64, BK,
+                        CU_TENSOR_MAP_SWIZZLE_128B);
+    if (rc != WMMA_OPS_OK) return rc;
+
+    switch (bn) {
+        case 64: rc = launch_gemm<64>(ta, tb, p, sms, stream); break;
+        case 128: rc = launch_gemm<128>(ta, tb, p, sms, stream); break;
+        default: rc = launch_gemm<256>(ta, tb, p, sms, stream); break;
+    }
+    if (rc != WMMA_OPS_OK) return rc;
+    if (split_k > 1) return launch_reduce(static_cast<const float*>(workspace), split_k);
+    return WMMA_OPS_OK;
+}
