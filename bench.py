@@ -1,0 +1,312 @@
+"""Benchmark of the GEMM hot path.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+    python -m torch.distributed.run --nnodes=1 --nproc-per-node N ... bench.py --gpus N ...
+
+One JSON line on stdout (rank 0). The headline metric is FP16 GEMM TFLOPS at 8192^3
+(A, B fp16, fp32 accumulate and output). A step is one 8192^3 product; at N > 1 every rank
+runs its own product (independent replicas, weak scaling, no collective on this path) and the
+sharded decoder-layer workload with its NCCL all-reduce is reported in the "layer" object.
+
+--impl reference times the reference's CPU path for the same product: fp32 torch.matmul on the
+host cores (the computation the reference's tests use as their oracle), on a bounded row slice.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import sys
+import threading
+import time
+from pathlib import Path
+
+import torch
+
+ROOT = Path(__file__).resolve().parent
+if str(ROOT) not in sys.path:
+    sys.path.insert(0, str(ROOT))
+
+GEMM_N = 8192
+# DRAM bytes (read + write) per 8192^3 launch of the dominant kernel, from one ncu capture
+# (profiles/gemm_f16f32_8192.md); None until captured.
+NCU_TRAFFIC_BYTES = {"gemm_8192": None}
+
+
+# ----------------------------------------------------------------------------- helpers
+def load_peaks():
+    p = ROOT / "MEASURED_PEAKS.json"
+    if p.exists():
+        d = json.loads(p.read_text())
+        return {"hbm_gbs": float(d["hbm_gbs"]), "tflops": float(d["bf16_tflops"]),
+                "tflops_sustained": float(d.get("bf16_tflops_sustained", d["bf16_tflops"])), "source": "measured"}
+    return {"hbm_gbs": 6650.0, "tflops": 1590.0, "tflops_sustained": 1400.0, "source": "fallback"}
+
+
+class ClockSampler:
+    """Samples SM clock and throttle reasons through NVML while the timed region runs (read-only)."""
+
+    def __init__(self, index: int, period_s: float = 0.002):
+        self.index, self.period = index, period_s
+        self.samples, self.reasons = [], set()
+        self.max_mhz = None
+        self._stop = threading.Event()
+        self._thread = None
+        try:
+            import pynvml
+            pynvml.nvmlInit()
+            self.nv = pynvml
+            self.h = pynvml.nvmlDeviceGetHandleByIndex(index)
+            self.max_mhz = pynvml.nvmlDeviceGetMaxClockInfo(self.h, pynvml.NVML_CLOCK_SM)
+        except Exception:
+            self.nv = None
+
+    def _run(self):
+        nv = self.nv
+        names = {}
+        for key in ("HwSlowdown", "HwThermalSlowdown", "SwThermalSlowdown", "SwPowerCap", "HwPowerBrakeSlowdown"):
+            v = getattr(nv, "nvmlClocksThrottleReason" + key, None) or getattr(nv, "nvmlClocksEventReason" + key, None)
+            if v is not None:
+                names[v] = key
+        while not self._stop.is_set():
+            try:
+                self.samples.append(nv.nvmlDeviceGetClockInfo(self.h, nv.NVML_CLOCK_SM))
+                mask = nv.nvmlDeviceGetCurrentClocksThrottleReasons(self.h)
+                for bit, key in names.items():
+                    if mask & bit:
+                        self.reasons.add(key)
+            except Exception:
+                pass
+            time.sleep(self.period)
+
+    def __enter__(self):
+        if self.nv is not None:
+            self._thread = threading.Thread(target=self._run, daemon=True)
+            self._thread.start()
+        return self
+
+    def __exit__(self, *a):
+        self._stop.set()
+        if self._thread is not None:
+            self._thread.join()
+
+    def summary(self):
+        if not self.samples:
+            return {"sm_mhz": None, "sm_max_mhz": self.max_mhz, "reasons": [], "samples": 0}
+        s = sorted(self.samples)
+        key_map = {"HwSlowdown": "hw_slowdown", "HwThermalSlowdown": "hw_thermal_slowdown",
+                   "SwThermalSlowdown": "sw_thermal_slowdown", "SwPowerCap": "sw_power_cap",
+                   "HwPowerBrakeSlowdown": "hw_power_brake_slowdown"}
+        return {"sm_mhz": s[len(s) // 2], "sm_max_mhz": self.max_mhz,
+                "reasons": sorted(key_map[r] for r in self.reasons), "samples": len(s)}
+
+
+def dist_env():
+    return int(os.environ.get("RANK", 0)), int(os.environ.get("LOCAL_RANK", 0)), int(os.environ.get("WORLD_SIZE", 1))
+
+
+def max_over_ranks(ms: float, world: int, dev) -> float:
+    if world == 1:
+        return ms
+    import torch.distributed as dist
+    t = torch.tensor([ms], dtype=torch.float64, device=dev)
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    return t.item()
+
+
+def barrier_sync(world: int):
+    if world > 1:
+        import torch.distributed as dist
+        dist.barrier()
+    torch.cuda.synchronize()
+
+
+def time_region(fn, steps: int, world: int, dev) -> float:
+    """ms per step of `steps` calls of fn, CUDA events on the launch stream, max over ranks."""
+    barrier_sync(world)
+    e0 = torch.cuda.Event(enable_timing=True)
+    e1 = torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(steps):
+        fn()
+    e1.record()
+    barrier_sync(world)
+    return max_over_ranks(e0.elapsed_time(e1), world, dev) / steps
+
+
+# ----------------------------------------------------------------------------- CPU arm
+def cpu_gemm_sample(target_s: float = 10.0, seed: int = 0):
+    """fp32 torch.matmul on the host cores on a row slice of the 8192^3 product.
+    Returns (tflops, rows, seconds, threads)."""
+    from oracle import gemm as og
+    n = GEMM_N
+    g = torch.Generator().manual_seed(seed)
+    B = torch.randn(n, n, generator=g).half()
+    probe_rows = 128
+    A = (torch.randn(probe_rows, n, generator=g) * n ** -0.5).half()
+    t0 = time.perf_counter()
+    og.gemm_ref(A, B)
+    dt = time.perf_counter() - t0
+    rate = 2.0 * probe_rows * n * n / dt
+    rows = int(min(n, max(probe_rows, (target_s * rate) / (2.0 * n * n))))
+    rows = max(128, rows // 128 * 128)
+    A = (torch.randn(rows, n, generator=g) * n ** -0.5).half()
+    reps, dt = 0, 0.0
+    t0 = time.perf_counter()
+    while dt < target_s and reps < 64:
+        og.gemm_ref(A, B)
+        reps += 1
+        dt = time.perf_counter() - t0
+    return 2.0 * reps * rows * n * n / dt / 1e12, rows, reps, dt, torch.get_num_threads()
+
+
+def run_reference_arm(args):
+    rank, _, world = dist_env()
+    if rank != 0:
+        return
+    from oracle import gemm as og
+    n = GEMM_N
+    g = torch.Generator().manual_seed(0)
+    B = torch.randn(n, n, generator=g).half()
+    A0 = (torch.randn(128, n, generator=g) * n ** -0.5).half()
+    t0 = time.perf_counter()
+    og.gemm_ref(A0, B)
+    rate = 2.0 * 128 * n * n / (time.perf_counter() - t0)
+    budget_s = 120.0 / max(1, args.steps + args.warmup)
+    rows = int(min(n, max(128, min(1.0, budget_s) * rate / (2.0 * n * n))))
+    rows = max(128, rows // 128 * 128)
+    A = (torch.randn(rows, n, generator=g) * n ** -0.5).half()
+    for _ in range(args.warmup):
+        og.gemm_ref(A, B)
+    t0 = time.perf_counter()
+    for _ in range(args.steps):
+        og.gemm_ref(A, B)
+    dt = (time.perf_counter() - t0) / args.steps
+    tflops = 2.0 * rows * n * n / dt / 1e12
+    threads = torch.get_num_threads()
+    sample = f"{rows} of {n} rows of A per step (fp32 torch.matmul on the host, inputs converted from fp16 each step)"
+    print(json.dumps({
+        "impl": "reference", "metric": "fp16_gemm_tflops_8192", "value": tflops, "unit": "TFLOP/s", "n_gpus": args.gpus,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": dt * 1e3, "higher_is_better": True,
+        "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": {"workload": "fp16_gemm_8192x8192x8192", "M": rows, "N": n, "K": n},
+        "cpu_baseline": {"value": tflops, "unit": "TFLOP/s", "cores": threads, "kind": "port", "sample": sample},
+        "e2e": {"value": tflops, "unit": "TFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+    }))
+
+
+# ----------------------------------------------------------------------------- GPU arm
+def run_ours(args):
+    import wmma_ops_b200 as w
+
+    rank, local_rank, world = dist_env()
+    dev = torch.device("cuda", local_rank)
+    torch.cuda.set_device(dev)
+    if world > 1:
+        import torch.distributed as dist
+        dist.init_process_group("nccl", device_id=dev)
+    peaks = load_peaks()
+    n = GEMM_N
+    flops = 2.0 * n * n * n
+
+    gen = torch.Generator(device=dev).manual_seed(1234 + rank)
+    A = (torch.randn(n, n, generator=gen, device=dev) * n ** -0.5).half()
+    B = torch.randn(n, n, generator=gen, device=dev).half()
+    tile_cfg, split_k = w.select_tile(n, n, n, torch.cuda.get_device_properties(dev).multi_processor_count)
+    launches_per_step = 1 if split_k <= 1 else 2
+
+    out = {}
+    if args.kernel_only:
+        # short device-only run for profilers: a few launches of one workload, no JSON line
+        run_kernel_only(args, w, dev, A, B)
+        return
+
+    def step():
+        out["C"] = w.matmul_adaptive(A, B)
+
+    for _ in range(max(args.warmup, 3)):
+        step()
+    torch.cuda.synchronize()
+    w.check_status(dev)
+    with ClockSampler(local_rank) as clocks:
+        ms = time_region(step, args.steps, world, dev)
+    w.check_status(dev)
+    value = world * flops / (ms * 1e-3) / 1e12
+
+    # ---- end to end through the public API: pinned host buffers in, host buffer out
+    hA = torch.empty((n, n), dtype=torch.float16).pin_memory()
+    hB = torch.empty((n, n), dtype=torch.float16).pin_memory()
+    hC = torch.empty((n, n), dtype=torch.float32).pin_memory()
+    hA.copy_(A)
+    hB.copy_(B)
+
+    def e2e_step():
+        dA = hA.to(dev, non_blocking=True)
+        dB = hB.to(dev, non_blocking=True)
+        hC.copy_(w.matmul_adaptive(dA, dB), non_blocking=True)
+
+    e2e_steps = max(3, min(args.steps, 10))
+    e2e_step()
+    e2e_ms = time_region(e2e_step, e2e_steps, world, dev)
+    e2e_value = world * flops / (e2e_ms * 1e-3) / 1e12
+
+    line = {
+        "metric": "fp16_gemm_tflops_8192", "value": value, "unit": "TFLOP/s", "n_gpus": world, "steps": args.steps,
+        "warmup": max(args.warmup, 3), "ms_per_step": ms, "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": "f16", "data": "synthetic",
+        "config": {"workload": "fp16_gemm_8192x8192x8192", "M": n, "N": n, "K": n, "tile_cfg": tile_cfg,
+                   "split_k": split_k, "l2": "inputs (2 x 128 MiB) and output (256 MiB) exceed the 126 MB L2",
+                   "parallelism": f"replicas x{world}" if world > 1 else "single"},
+        "clocks": clocks.summary(),
+        "e2e": {"value": e2e_value, "unit": "TFLOP/s", "h2d_bytes_per_step": 2 * n * n * 2, "d2h_bytes_per_step": n * n * 4,
+                "ms_per_step": e2e_ms, "steps": e2e_steps},
+        "gpu_launches": launches_per_step * args.steps,
+    }
+    per_gpu = flops / (ms * 1e-3) / 1e12
+    line["roofline"] = {"bound": "tensor", "achieved": per_gpu, "peak": peaks["tflops"], "unit": "TFLOP/s",
+                        "frac": per_gpu / peaks["tflops"], "traffic": NCU_TRAFFIC_BYTES["gemm_8192"],
+                        "peak_source": f"{peaks['source']} cuBLAS bf16 burst",
+                        "frac_of_sustained": per_gpu / peaks["tflops_sustained"],
+                        "frac_of_nominal_2250": per_gpu / 2250.0}
+    if rank == 0 and world == 1:
+        tflops, rows, reps, secs, threads = cpu_gemm_sample()
+        line["cpu_baseline"] = {"value": tflops, "unit": "TFLOP/s", "cores": threads, "kind": "port",
+                                "sample": f"{reps} x ({rows} of {n} rows of A against the full B), {secs:.1f} s of fp32 "
+                                          "torch.matmul on the host"}
+    extras = getattr(sys.modules[__name__], "extra_measurements", None)
+    if extras is not None:
+        line.update(extras(args, w, dev, rank, world, peaks))
+    if rank == 0:
+        print(json.dumps(line))
+    if world > 1:
+        import torch.distributed as dist
+        dist.barrier()
+        dist.destroy_process_group()
+
+
+def run_kernel_only(args, w, dev, A, B):
+    if args.kernel_only == "gemm":
+        for _ in range(3):
+            w.matmul_adaptive(A, B)
+    else:
+        raise SystemExit(f"unknown --kernel-only {args.kernel_only}")
+    torch.cuda.synchronize()
+    w.check_status(dev)
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--kernel-only", default="", help="profiling aid: launch one workload a few times and exit")
+    args = ap.parse_args()
+    if args.impl == "reference":
+        run_reference_arm(args)
+    else:
+        run_ours(args)
+
+
+if __name__ == "__main__":
+    main()

@@ -1,0 +1,71 @@
+"""INT4 weight format "W4-B200-v1" and W4A16 arithmetic on the CPU. TEST INFRASTRUCTURE.
+
+PARITY UNPINNED: the reference tree contains no INT4 / W4A16 code, so there is nothing of the
+reference to check this against; this file is the written specification the CUDA prepack,
+unpack and dequant kernels must match bit for bit.
+
+Format
+  codes    uint8 [K, N], values 0..15; weight[k, n] = (code[k, n] - 8) * scale[k // g, n]
+  scales   fp16 [K // g, N] (g = group size along K, 128 in the configs)
+  qweight  uint32 [N, K // 8]; word (n, j) holds k = 8j .. 8j+7 of column n; nibble p
+           (bits 4p .. 4p+3) holds k = 8j + NIBBLE_K[p], NIBBLE_K = (0, 2, 4, 6, 1, 3, 5, 7).
+           With this order `(word >> 4i) & 0x000F000F` yields the adjacent pair (k=8j+2i, 8j+2i+1)
+           in the low / high half-word, which is what a half2 dequant wants.
+"""
+from __future__ import annotations
+
+import numpy as np
+import torch
+
+NIBBLE_K = (0, 2, 4, 6, 1, 3, 5, 7)
+ZERO_POINT = 8
+
+
+def pack_ref(codes: torch.Tensor) -> torch.Tensor:
+    """codes uint8 [K,N] -> qweight int32 [N, K//8] (bit pattern of the uint32 words)."""
+    c = codes.detach().cpu().numpy().astype(np.uint32)
+    K, N = c.shape
+    assert K % 8 == 0 and c.max(initial=0) <= 15
+    ct = c.T.reshape(N, K // 8, 8)  # [n, j, k_in_word]
+    words = np.zeros((N, K // 8), dtype=np.uint32)
+    for p, kk in enumerate(NIBBLE_K):
+        words |= ct[:, :, kk] << np.uint32(4 * p)
+    return torch.from_numpy(words.view(np.int32).copy())
+
+
+def unpack_ref(qweight: torch.Tensor, K: int, N: int) -> torch.Tensor:
+    """qweight int32 [N, K//8] -> codes uint8 [K,N]."""
+    w = qweight.detach().cpu().numpy().view(np.uint32).reshape(N, K // 8)
+    ct = np.zeros((N, K // 8, 8), dtype=np.uint8)
+    for p, kk in enumerate(NIBBLE_K):
+        ct[:, :, kk] = ((w >> np.uint32(4 * p)) & np.uint32(0xF)).astype(np.uint8)
+    return torch.from_numpy(ct.reshape(N, K).T.copy())
+
+
+def dequant_ref(codes: torch.Tensor, scales: torch.Tensor, group_size: int = 128) -> torch.Tensor:
+    """W fp16 [K,N] = fp16(code - 8) * scale[k // g, n], a single fp16 multiply rounded to
+    nearest even (computed in fp32 and rounded once: the product of two fp16 values is exact in
+    fp32, so one rounding to fp16 equals the IEEE fp16 multiply)."""
+    K, N = codes.shape
+    q = (codes.detach().cpu().to(torch.int32) - ZERO_POINT).to(torch.float32)
+    s = scales.detach().cpu().to(torch.float32).repeat_interleave(group_size, dim=0)[:K]
+    return (q * s).to(torch.float16)
+
+
+def w4a16_ref(A: torch.Tensor, codes: torch.Tensor, scales: torch.Tensor, group_size: int = 128) -> torch.Tensor:
+    """C fp32 [M,N] = A.float() @ dequant(codes, scales).float()."""
+    W = dequant_ref(codes, scales, group_size)
+    return torch.matmul(A.detach().cpu().float(), W.float())
+
+
+def seeded_w4(K: int, N: int, group_size: int = 128, seed: int = 7):
+    """codes uniform in [0,15], scales fp16 uniform in [0.001, 0.02] (the W4A16 config)."""
+    g = torch.Generator().manual_seed(seed)
+    codes = torch.randint(0, 16, (K, N), generator=g, dtype=torch.uint8)
+    scales = (torch.rand(K // group_size, N, generator=g) * (0.02 - 0.001) + 0.001).to(torch.float16)
+    return codes, scales
+
+
+def w4a16_bytes(M: int, N: int, K: int, group_size: int = 128) -> int:
+    """Algorithmic bytes of one W4A16 product: packed weights + scales + activations + fp32 output."""
+    return K * N // 2 + 2 * (K // group_size) * N + 2 * M * K + 4 * M * N
