@@ -7,10 +7,13 @@ unpack and dequant kernels must match bit for bit.
 Format
   codes    uint8 [K, N], values 0..15; weight[k, n] = (code[k, n] - 8) * scale[k // g, n]
   scales   fp16 [K // g, N] (g = group size along K, 128 in the configs)
-  qweight  uint32 [N, K // 8]; word (n, j) holds k = 8j .. 8j+7 of column n; nibble p
-           (bits 4p .. 4p+3) holds k = 8j + NIBBLE_K[p], NIBBLE_K = (0, 2, 4, 6, 1, 3, 5, 7).
-           With this order `(word >> 4i) & 0x000F000F` yields the adjacent pair (k=8j+2i, 8j+2i+1)
-           in the low / high half-word, which is what a half2 dequant wants.
+  qweight  uint32 [ceil(N/128), K // 64, 128, 8]: block (nt, kb) is 4 KB and holds, for the 128
+           columns n = 128 nt + r (zero codes where n >= N), the codes k = 64 kb .. 64 kb + 63 as
+           8 words per column; word j, nibble p (bits 4p .. 4p+3) holds
+           k = 64 kb + 8 j + NIBBLE_K[p], NIBBLE_K = (0, 2, 4, 6, 1, 3, 5, 7).
+           With this nibble order `(word >> 4i) & 0x000F000F` yields the adjacent pair
+           (k = 8j+2i, 8j+2i+1) in the low / high half-word, which is what a half2 dequant wants;
+           with this block order one column tile is a contiguous run of 4 KB blocks along K.
 """
 from __future__ import annotations
 
@@ -22,24 +25,31 @@ ZERO_POINT = 8
 
 
 def pack_ref(codes: torch.Tensor) -> torch.Tensor:
-    """codes uint8 [K,N] -> qweight int32 [N, K//8] (bit pattern of the uint32 words)."""
+    """codes uint8 [K,N] -> qweight int32 [ceil(N/128), K//64, 128, 8] (bit pattern of uint32 words)."""
     c = codes.detach().cpu().numpy().astype(np.uint32)
     K, N = c.shape
-    assert K % 8 == 0 and c.max(initial=0) <= 15
-    ct = c.T.reshape(N, K // 8, 8)  # [n, j, k_in_word]
-    words = np.zeros((N, K // 8), dtype=np.uint32)
+    assert K % 64 == 0 and c.max(initial=0) <= 15
+    n_pad = -(-N // 128) * 128
+    cp = np.zeros((K, n_pad), dtype=np.uint32)
+    cp[:, :N] = c
+    # [kb, j, kk, nt, r] -> [nt, kb, r, j, kk]
+    t = cp.reshape(K // 64, 8, 8, n_pad // 128, 128).transpose(3, 0, 4, 1, 2)
+    words = np.zeros(t.shape[:4], dtype=np.uint32)
     for p, kk in enumerate(NIBBLE_K):
-        words |= ct[:, :, kk] << np.uint32(4 * p)
-    return torch.from_numpy(words.view(np.int32).copy())
+        words |= t[..., kk] << np.uint32(4 * p)
+    return torch.from_numpy(np.ascontiguousarray(words).view(np.int32))
 
 
 def unpack_ref(qweight: torch.Tensor, K: int, N: int) -> torch.Tensor:
-    """qweight int32 [N, K//8] -> codes uint8 [K,N]."""
-    w = qweight.detach().cpu().numpy().view(np.uint32).reshape(N, K // 8)
-    ct = np.zeros((N, K // 8, 8), dtype=np.uint8)
+    """qweight int32 [ceil(N/128), K//64, 128, 8] -> codes uint8 [K,N]."""
+    n_tiles = -(-N // 128)
+    w = qweight.detach().cpu().numpy().view(np.uint32).reshape(n_tiles, K // 64, 128, 8)
+    t = np.zeros((n_tiles, K // 64, 128, 8, 8), dtype=np.uint8)
     for p, kk in enumerate(NIBBLE_K):
-        ct[:, :, kk] = ((w >> np.uint32(4 * p)) & np.uint32(0xF)).astype(np.uint8)
-    return torch.from_numpy(ct.reshape(N, K).T.copy())
+        t[..., kk] = ((w >> np.uint32(4 * p)) & np.uint32(0xF)).astype(np.uint8)
+    # [nt, kb, r, j, kk] -> [kb, j, kk, nt, r]
+    c = t.transpose(1, 3, 4, 0, 2).reshape(K, n_tiles * 128)
+    return torch.from_numpy(np.ascontiguousarray(c[:, :N]))
 
 
 def dequant_ref(codes: torch.Tensor, scales: torch.Tensor, group_size: int = 128) -> torch.Tensor:

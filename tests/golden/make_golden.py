@@ -61,7 +61,7 @@ def gemm_cases():
 
 
 def int4_cases():
-    codes, scales = int4.seeded_w4(128, 24, 64, seed=5)
+    codes, scales = int4.seeded_w4(128, 136, 64, seed=5)
     q = int4.pack_ref(codes)
     w = int4.dequant_ref(codes, scales, 64)
     np.savez_compressed(HERE / "int4_golden.npz", codes=codes.numpy(), scales=scales.numpy(),

@@ -1,0 +1,139 @@
+"""INT4 prepack (bit-exact) and fused W4A16 GEMM parity on the GPU.
+
+The packed format and the dequant arithmetic are this repository's specification
+(oracle/int4.py; the reference tree has no INT4 code). Pack / unpack / dequant must match the
+oracle bit for bit; the GEMM must be within relative Frobenius error 1e-3 of the fp32 oracle."""
+import numpy as np
+import pytest
+import torch
+
+import wmma_ops_b200 as w
+from oracle import gemm as og
+from oracle import int4
+
+pytestmark = pytest.mark.gpu
+TOL = 1e-3
+
+
+def _sync_ok():
+    torch.cuda.synchronize()
+    w.check_status()
+
+
+def test_golden_pack_unpack_dequant_bit_exact(cuda, golden_dir):
+    g = np.load(golden_dir / "int4_golden.npz")
+    codes = torch.from_numpy(g["codes"])
+    scales = torch.from_numpy(g["scales"])
+    group = int(g["group"])
+    q, sc = w.int4_prepack(codes.to(cuda), scales.to(cuda), group)
+    _sync_ok()
+    assert q.dtype == torch.int32 and tuple(q.shape) == tuple(g["qweight"].shape)
+    assert np.array_equal(q.cpu().numpy(), g["qweight"])
+    assert torch.equal(w.int4_unpack(q, codes.shape[1]).cpu(), codes)
+    W = w.int4_dequant(q, sc, group).cpu()
+    assert np.array_equal(W.numpy().view(np.uint16), g["W"].view(np.uint16))
+
+
+@pytest.mark.parametrize("shape", [(64, 8, 64), (128, 136, 64), (256, 128, 128), (4096, 11008, 128)])
+def test_pack_roundtrip_bit_exact(cuda, shape):
+    K, N, group = shape
+    codes, scales = int4.seeded_w4(K, N, group, seed=5)
+    q, sc = w.int4_prepack(codes.to(cuda), scales.to(cuda), group)
+    _sync_ok()
+    assert torch.equal(q.cpu(), int4.pack_ref(codes))
+    assert torch.equal(w.int4_unpack(q, N).cpu(), codes)
+    W = w.int4_dequant(q, sc, group).cpu()
+    assert torch.equal(W.view(torch.int16), int4.dequant_ref(codes, scales, group).view(torch.int16))
+
+
+def test_all_code_scale_products_bit_exact(cuda):
+    # every code against a spread of scale bit patterns, including subnormal products
+    K, N = 64, 2048
+    codes = (torch.arange(K)[:, None] % 16).to(torch.uint8).expand(K, N).contiguous()
+    bits = torch.linspace(1, 0x3BFF, N).to(torch.int16)      # positive fp16 up to just below 1.0
+    scales = bits.view(torch.float16)[None, :].contiguous()
+    q, sc = w.int4_prepack(codes.to(cuda), scales.to(cuda), 64)
+    W = w.int4_dequant(q, sc, 64).cpu()
+    _sync_ok()
+    assert torch.equal(W.view(torch.int16), int4.dequant_ref(codes, scales, 64).view(torch.int16))
+
+
+def _w4_case(cuda, M, N, K, group, split, seed=1):
+    codes, scales = int4.seeded_w4(K, N, group, seed=seed)
+    A, _ = og.seeded_ab(M, 8, K, seed=seed + 1)
+    q, sc = w.int4_prepack(codes.to(cuda), scales.to(cuda), group)
+    C = w.matmul_w4a16(A.to(cuda), q, sc, group, split)
+    _sync_ok()
+    assert C.dtype == torch.float32 and tuple(C.shape) == (M, N)
+    return og.rel_frobenius(C, int4.w4a16_ref(A, codes, scales, group))
+
+
+@pytest.mark.parametrize("case", [
+    (16, 128, 64, 64, 1), (1, 128, 256, 128, 1), (16, 256, 512, 128, 2), (3, 264, 1024, 128, 4),
+    (32, 128, 256, 128, 1), (64, 384, 256, 64, 1), (100, 8, 128, 128, 1), (128, 256, 512, 128, 1),
+    (256, 256, 512, 128, 1), (300, 136, 256, 128, 1), (512, 1024, 1024, 128, 1), (17, 1000, 2048, 256, 3),
+])
+def test_w4a16_small_and_ragged(cuda, case):
+    M, N, K, group, split = case
+    assert _w4_case(cuda, M, N, K, group, split) < TOL
+
+
+@pytest.mark.parametrize("M", [1, 16, 128])
+def test_config3_decode_shapes(cuda, M):
+    assert _w4_case(cuda, M, 11008, 4096, 128, 0) < TOL
+
+
+def test_config3_prefill_shape_repeated(cuda):
+    # M = 4096: every CTA walks several tiles; repeated to catch timing-dependent faults
+    M, N, K, group = 4096, 11008, 4096, 128
+    codes, scales = int4.seeded_w4(K, N, group, seed=1)
+    A, _ = og.seeded_ab(M, 8, K, seed=2)
+    q, sc = w.int4_prepack(codes.to(cuda), scales.to(cuda), group)
+    ref = int4.w4a16_ref(A, codes, scales, group)
+    Ad = A.to(cuda)
+    first = None
+    for _ in range(6):
+        C = w.matmul_w4a16(Ad, q, sc, group)
+        _sync_ok()
+        assert og.rel_frobenius(C, ref) < TOL
+        first = C if first is None else first
+        assert torch.equal(C, first)          # deterministic
+
+
+def test_split_k_is_deterministic_and_reusable(cuda):
+    codes, scales = int4.seeded_w4(4096, 1024, 128, seed=3)
+    A, _ = og.seeded_ab(2, 8, 4096, seed=4)
+    q, sc = w.int4_prepack(codes.to(cuda), scales.to(cuda), 128)
+    ref = int4.w4a16_ref(A, codes, scales, 128)
+    outs = [w.matmul_w4a16(A.to(cuda), q, sc, 128, 4) for _ in range(3)]   # arrival counters reset themselves
+    _sync_ok()
+    assert og.rel_frobenius(outs[0], ref) < TOL
+    assert torch.equal(outs[0], outs[1]) and torch.equal(outs[1], outs[2])
+
+
+def test_fused_matches_dequant_then_dense_gemm(cuda):
+    # the fused kernel and (dequant to fp16, then the dense tcgen05 GEMM) see the same fp16 weights
+    codes, scales = int4.seeded_w4(1024, 512, 128, seed=6)
+    A, _ = og.seeded_ab(200, 8, 1024, seed=7)
+    q, sc = w.int4_prepack(codes.to(cuda), scales.to(cuda), 128)
+    fused = w.matmul_w4a16(A.to(cuda), q, sc, 128)
+    two_pass = w.matmul(A.to(cuda), w.int4_dequant(q, sc, 128))
+    _sync_ok()
+    assert og.rel_frobenius(fused, two_pass.cpu()) < 1e-5
+
+
+def test_w4a16_errors(cuda):
+    codes, scales = int4.seeded_w4(256, 128, 128, seed=8)
+    q, sc = w.int4_prepack(codes.to(cuda), scales.to(cuda), 128)
+    A = torch.randn(4, 256, device=cuda).half()
+    with pytest.raises(RuntimeError, match="Inputs must be float16"):
+        w.matmul_w4a16(A.float(), q, sc, 128)
+    with pytest.raises(RuntimeError, match="Inner dimensions must match"):
+        w.matmul_w4a16(A[:, :128].contiguous(), q, sc, 128)
+    with pytest.raises(RuntimeError, match="codes must be uint8"):
+        w.int4_prepack(codes.to(cuda).int(), scales.to(cuda), 128)
+    with pytest.raises(RuntimeError, match="K must be a positive multiple of 64"):
+        w.int4_prepack(codes[:32].to(cuda), scales[:1].to(cuda), 32)
+    with pytest.raises(RuntimeError, match="scales do not match"):
+        w.matmul_w4a16(A, q, sc, 64)
+    assert w.matmul_w4a16(A[:0], q, sc, 128).shape == (0, 128)

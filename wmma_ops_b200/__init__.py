@@ -31,4 +31,6 @@ from .ops import (  # noqa: F401
     select_tile,
 )
 
+from .quant import int4_dequant, int4_prepack, int4_unpack, matmul_w4a16  # noqa: F401,E402
+
 __version__ = "0.1.0"

@@ -114,7 +114,7 @@ gemm_f16f32_kernel(const __grid_constant__ CUtensorMap tmap_a,
     __syncthreads();
     tc_fence_after_sync();
     uint32_t tmem_base;
-    asm volatile("ld.shared.u32 %0, [%1];" : "=r"(tmem_base) : "r"(tmem_slot));
+    asm volatile("ld.shared.u32 %0, [%1];" : "=r"(tmem_base) : "r"(tmem_slot) : "memory");
 
     const int total_units = p.m_blocks * p.n_blocks * p.split_k;
 

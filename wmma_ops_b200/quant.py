@@ -1,0 +1,113 @@
+"""INT4 prepack and W4A16 matmul entry points.
+
+The reference snapshot has neither (its README and sources contain no INT4 code), so names,
+packed format ("W4-B200-v1", described in include/wmma_ops_b200.h) and arithmetic are defined
+by this package:  weight[k, n] = (code[k, n] - 8) * scale[k // group_size, n],  C = A @ weight
+with fp16 operands and fp32 accumulation.
+"""
+from __future__ import annotations
+
+from typing import Tuple
+
+import torch
+
+from . import _lib
+from .ops import _post, _require, _sm_count, _status_word, _stream, _workspace
+
+ZERO_POINT = 8
+
+
+def _check_codes(codes: torch.Tensor, scales: torch.Tensor, group_size: int) -> Tuple[int, int]:
+    _require(codes.is_cuda and scales.is_cuda, "Inputs must be CUDA tensors")
+    _require(codes.device == scales.device, "Inputs must be on same device")
+    _require(codes.dtype == torch.uint8, "codes must be uint8 with values 0..15")
+    _require(scales.dtype == torch.float16, "scales must be float16")
+    _require(codes.dim() == 2 and scales.dim() == 2, "codes and scales must be 2D")
+    K, N = codes.shape
+    _require(group_size > 0 and K % group_size == 0, f"group_size must divide K (got group_size={group_size}, K={K})")
+    _require(tuple(scales.shape) == (K // group_size, N),
+             f"scales must have shape [K/group_size, N] = [{K // group_size}, {N}]")
+    return K, N
+
+
+def int4_prepack(codes: torch.Tensor, scales: torch.Tensor, group_size: int = 128,
+                 zero_point: int = ZERO_POINT) -> Tuple[torch.Tensor, torch.Tensor]:
+    """Packs uint8 codes [K,N] (0..15) into the kernel's layout.
+
+    Returns (qweight int32 [ceil(N/128), K/64, 128, 8], scales fp16 [K/group_size, N] contiguous)."""
+    _require(zero_point == ZERO_POINT, "only zero_point=8 is supported")
+    K, N = _check_codes(codes, scales, group_size)
+    codes = codes.contiguous()
+    dev = codes.device
+    q = torch.empty(((N + 127) // 128, K // 64, 128, 8), dtype=torch.int32, device=dev)
+    with torch.cuda.device(dev):
+        _lib.check(_lib.load().wmma_ops_int4_prepack(codes.data_ptr(), q.data_ptr(), K, N, _stream(dev)))
+    return q, scales.contiguous()
+
+
+def _qshape(qweight: torch.Tensor, N: int) -> Tuple[int, int]:
+    _require(qweight.is_cuda and qweight.dtype == torch.int32 and qweight.dim() == 4
+             and qweight.size(2) == 128 and qweight.size(3) == 8 and qweight.is_contiguous(),
+             "qweight must be a contiguous CUDA int32 tensor [ceil(N/128), K/64, 128, 8] from int4_prepack")
+    _require(qweight.size(0) == (N + 127) // 128, "qweight does not match N")
+    return qweight.size(1) * 64, N
+
+
+def int4_unpack(qweight: torch.Tensor, N: int) -> torch.Tensor:
+    """Inverse of int4_prepack: codes uint8 [K,N]."""
+    K, N = _qshape(qweight, N)
+    dev = qweight.device
+    out = torch.empty((K, N), dtype=torch.uint8, device=dev)
+    with torch.cuda.device(dev):
+        _lib.check(_lib.load().wmma_ops_int4_unpack(qweight.data_ptr(), out.data_ptr(), K, N, _stream(dev)))
+    return out
+
+
+def int4_dequant(qweight: torch.Tensor, scales: torch.Tensor, group_size: int = 128) -> torch.Tensor:
+    """fp16 weights [K,N] = fp16(code - 8) * scale, one fp16 multiply per element."""
+    _require(scales.is_cuda and scales.dtype == torch.float16 and scales.dim() == 2, "scales must be CUDA float16 2D")
+    K, N = _qshape(qweight, scales.size(1))
+    _require(scales.size(0) * group_size == K, "scales do not match K / group_size")
+    dev = qweight.device
+    out = torch.empty((K, N), dtype=torch.float16, device=dev)
+    with torch.cuda.device(dev):
+        _lib.check(_lib.load().wmma_ops_int4_dequant(qweight.data_ptr(), scales.contiguous().data_ptr(),
+                                                     out.data_ptr(), K, N, group_size, _stream(dev)))
+    return out
+
+
+def matmul_w4a16(A: torch.Tensor, qweight: torch.Tensor, scales: torch.Tensor, group_size: int = 128,
+                 split_k: int = 0) -> torch.Tensor:
+    """C fp32 [M,N] = A fp16 [M,K] @ dequant(qweight, scales); the weights are expanded to fp16
+    inside the kernel's shared memory. split_k=0 lets the library choose."""
+    _require(A.is_cuda and qweight.is_cuda and scales.is_cuda, "Inputs must be CUDA tensors")
+    _require(A.device == qweight.device and A.device == scales.device, "Inputs must be on same device")
+    _require(A.dtype == torch.float16, "Inputs must be float16")
+    _require(scales.dtype == torch.float16 and scales.dim() == 2, "scales must be float16 [K/group_size, N]")
+    _require(A.dim() == 2, "Inputs must be 2D")
+    N = scales.size(1)
+    K, N = _qshape(qweight, N)
+    _require(A.size(1) == K, "Inner dimensions must match")
+    _require(scales.size(0) * group_size == K, "scales do not match K / group_size")
+    A = A.contiguous()
+    scales = scales.contiguous()
+    _require(A.data_ptr() % 16 == 0, "A must be 16-byte aligned")
+    M = A.size(0)
+    dev = A.device
+    lib = _lib.load()
+    C = torch.empty((M, N), dtype=torch.float32, device=dev)
+    if M == 0:
+        return C
+    with torch.cuda.device(dev):
+        if split_k == 0:
+            split_k = lib.wmma_ops_w4a16_select_split(M, N, K, _sm_count(dev))
+        ws_ptr, ws_bytes = None, 0
+        if split_k > 1:
+            need = lib.wmma_ops_w4a16_workspace_bytes(M, N, K, split_k)
+            ws = _workspace(dev, need, zero_init=True)
+            ws_ptr, ws_bytes = ws.data_ptr(), ws.numel()
+        rc = lib.wmma_ops_w4a16_gemm(A.data_ptr(), qweight.data_ptr(), scales.data_ptr(), C.data_ptr(), M, N, K,
+                                     group_size, split_k, ws_ptr, ws_bytes, _status_word(dev).data_ptr(), _stream(dev))
+        _lib.check(rc)
+        _post(dev)
+    return C
