@@ -1,3 +1,396 @@
-// placeholder until the attention kernel lands
+// Flash-attention forward for sm_100a: O = softmax(scale * Q K^T [+ causal mask]) V.
+//
+// Implements the signature the reference documents, flash_attention(Q, K, V, causal, scale) with
+// Q, K, V [B,H,N,D] fp16 (README.md:221-251); the reference's own kernel is not in its tree, so
+// the arithmetic follows the fp32 softmax-attention oracle.
+//
+// One CTA owns 128 query rows of one (batch, head) and walks the key/value sequence in tiles
+// of 128 with an online softmax:
+//   warp 0      TMA producer: Q once, then K and V tiles into two-stage rings
+//   warp 1      TMEM owner and MMA issuer: S = Q K^T (fp32, TMEM), O += P V (fp32, TMEM)
+//   warps 2..5  softmax: one query row per thread; read S from TMEM, keep the running max and
+//               sum, write P (fp16) into 128-byte-swizzled shared memory as the A operand of
+//               P V, rescale O in TMEM when the max moved, and at the end store O / l as fp16.
+// Two S accumulators and two P buffers let Q K^T of tile i+1 run on the tensor cores while the
+// softmax warps work on tile i. K is a K-major operand; V, read as [kv, d] with d contiguous,
+// is an MN-major operand, so neither is transposed.
 #include "host_common.cuh"
-extern "C" int wmma_ops_fmha_fwd(const void*, const void*, const void*, void*, int, int, int, int, float, int, int*, void*) { wb::set_error("not built"); return WMMA_OPS_ERR_UNSUPPORTED; }
+#include "ptx.cuh"
+
+namespace wb {
+
+constexpr int FA_BM = 128;  // query rows per CTA
+constexpr int FA_BN = 128;  // keys per tile
+constexpr int FA_THREADS = 192;
+
+template <int D>
+struct FaCfg {
+    static constexpr int DB = D / 64;                   // 64-wide head-dim blocks
+    static constexpr int TILE_BYTES = 128 * D * 2;      // Q, K or V tile
+    static constexpr int BOX_BYTES = 128 * 64 * 2;      // one [128 rows x 64 halves] box
+    static constexpr int P_BYTES = FA_BM * FA_BN * 2;   // one P buffer
+    static constexpr int SMEM_BYTES = 5 * TILE_BYTES + 2 * P_BYTES + 1024 + 256;
+    static constexpr int TMEM_COLS = 512;
+    static constexpr int S_COL0 = 0, S_COL1 = 128, O_COL = 256;
+};
+
+struct FaParams {
+    __half* O;
+    int B, H, S, D;
+    float scale_log2;  // scale * log2(e)
+    int causal;
+    int* status;
+};
+
+__device__ __forceinline__ void fa_report(int* status, int role, int detail) {
+    if (status != nullptr && atomicCAS(status, 0, 3) == 0) {
+        status[1] = role;
+        status[2] = static_cast<int>(blockIdx.x + gridDim.x * blockIdx.y);
+        status[3] = detail;
+    }
+}
+
+__device__ __forceinline__ float fast_exp2(float x) {
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
+
+__device__ __forceinline__ uint32_t pack_half2(float a, float b) {
+    const __half2 h = __floats2half2_rn(a, b);
+    return *reinterpret_cast<const uint32_t*>(&h);
+}
+
+template <int D>
+__global__ void __launch_bounds__(FA_THREADS, 1)
+fmha_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ CUtensorMap tmap_k,
+                const __grid_constant__ CUtensorMap tmap_v, const FaParams p) {
+    using Cfg = FaCfg<D>;
+    extern __shared__ uint8_t fa_smem_raw[];
+    const uint32_t smem_base = (smem_u32(fa_smem_raw) + 1023u) & ~1023u;
+    const uint32_t q_smem = smem_base;
+    auto k_smem = [&](int s) { return smem_base + (1 + s) * Cfg::TILE_BYTES; };
+    auto v_smem = [&](int s) { return smem_base + (3 + s) * Cfg::TILE_BYTES; };
+    auto p_smem = [&](int s) { return smem_base + 5 * Cfg::TILE_BYTES + s * Cfg::P_BYTES; };
+    const uint32_t bar_base = smem_base + 5 * Cfg::TILE_BYTES + 2 * Cfg::P_BYTES;
+    const uint32_t q_full = bar_base;
+    auto k_full = [&](int s) { return bar_base + 8u * (1 + s); };
+    auto k_empty = [&](int s) { return bar_base + 8u * (3 + s); };
+    auto v_full = [&](int s) { return bar_base + 8u * (5 + s); };
+    auto v_empty = [&](int s) { return bar_base + 8u * (7 + s); };
+    auto s_full = [&](int s) { return bar_base + 8u * (9 + s); };
+    auto s_empty = [&](int s) { return bar_base + 8u * (11 + s); };
+    auto p_ready = [&](int s) { return bar_base + 8u * (13 + s); };
+    const uint32_t pv_done = bar_base + 8u * 15;
+    const uint32_t tmem_slot = bar_base + 8u * 16;
+
+    const int warp = threadIdx.x >> 5;
+    const int lane = threadIdx.x & 31;
+
+    // Heavy (late) query tiles first when causal, so the tail of the grid is made of short CTAs.
+    const int q_tiles = gridDim.x;
+    const int q_tile = p.causal ? (q_tiles - 1 - static_cast<int>(blockIdx.x)) : static_cast<int>(blockIdx.x);
+    const int bh = blockIdx.y;
+    const int q0 = q_tile * FA_BM;
+    const int kv_tiles_all = (p.S + FA_BN - 1) / FA_BN;
+    const int n_tiles = p.causal ? min(kv_tiles_all, (q0 + FA_BM - 1) / FA_BN + 1) : kv_tiles_all;
+
+    if (threadIdx.x == 0) {
+        mbar_init(q_full, 1);
+        for (int s = 0; s < 2; ++s) {
+            mbar_init(k_full(s), 1);
+            mbar_init(k_empty(s), 1);
+            mbar_init(v_full(s), 1);
+            mbar_init(v_empty(s), 1);
+            mbar_init(s_full(s), 1);
+            mbar_init(s_empty(s), 128);
+            mbar_init(p_ready(s), 128);
+        }
+        mbar_init(pv_done, 1);
+        fence_barrier_init();
+        fence_proxy_async_smem();
+        prefetch_tmap(&tmap_q);
+        prefetch_tmap(&tmap_k);
+        prefetch_tmap(&tmap_v);
+    }
+    if (warp == 1) {
+        tmem_alloc(tmem_slot, Cfg::TMEM_COLS);
+        tmem_relinquish();
+    }
+    tc_fence_before_sync();
+    __syncthreads();
+    tc_fence_after_sync();
+    uint32_t tmem_base;
+    asm volatile("ld.shared.u32 %0, [%1];" : "=r"(tmem_base) : "r"(tmem_slot) : "memory");
+
+    if (warp == 0) {
+        // ------------------------------------------------------------ TMA producer
+        if (lane == 0) {
+            mbar_arrive_expect_tx(q_full, Cfg::TILE_BYTES);
+#pragma unroll
+            for (int b = 0; b < Cfg::DB; ++b)
+                tma_load_3d(q_smem + b * Cfg::BOX_BYTES, &tmap_q, q_full, b * 64, q0, bh);
+            for (int i = 0; i < n_tiles; ++i) {
+                const int s = i & 1;
+                const uint32_t ph = (i >> 1) & 1;
+                if (!mbar_wait(k_empty(s), ph ^ 1u)) {
+                    fa_report(p.status, 0, i);
+                    break;
+                }
+                mbar_arrive_expect_tx(k_full(s), Cfg::TILE_BYTES);
+#pragma unroll
+                for (int b = 0; b < Cfg::DB; ++b)
+                    tma_load_3d(k_smem(s) + b * Cfg::BOX_BYTES, &tmap_k, k_full(s), b * 64, i * FA_BN, bh);
+                if (!mbar_wait(v_empty(s), ph ^ 1u)) {
+                    fa_report(p.status, 0, -i - 1);
+                    break;
+                }
+                mbar_arrive_expect_tx(v_full(s), Cfg::TILE_BYTES);
+#pragma unroll
+                for (int b = 0; b < Cfg::DB; ++b)
+                    tma_load_3d(v_smem(s) + b * Cfg::BOX_BYTES, &tmap_v, v_full(s), b * 64, i * FA_BN, bh);
+            }
+        }
+    } else if (warp == 1) {
+        // ------------------------------------------------------------ MMA issuer
+        if (lane == 0) {
+            constexpr uint32_t idesc_s = make_idesc_f16_f32(FA_BM, FA_BN, false, false);
+            constexpr uint32_t idesc_o = make_idesc_f16_f32(FA_BM, D, false, true);
+            bool ok = mbar_wait(q_full, 0);
+            if (!ok) fa_report(p.status, 1, -1);
+            auto issue_pv = [&](int i) -> bool {
+                const int s = i & 1;
+                const uint32_t ph = (i >> 1) & 1;
+                if (!mbar_wait(v_full(s), ph) || !mbar_wait(p_ready(s), ph)) {
+                    fa_report(p.status, 1, 1000 + i);
+                    return false;
+                }
+                tc_fence_after_sync();
+#pragma unroll
+                for (int kk = 0; kk < FA_BN / 16; ++kk) {
+                    // P: K-major, 64 keys per 16 KB block, 32 bytes per 16 keys inside a block
+                    const uint64_t a_desc =
+                        make_smem_desc_sw128(p_smem(s) + (kk >> 2) * Cfg::BOX_BYTES + (kk & 3) * 32, 16, 1024);
+                    // V: MN-major, 16 keys = 2048 bytes further; 64-wide d blocks BOX_BYTES apart
+                    const uint64_t b_desc = make_smem_desc_sw128(v_smem(s) + kk * 2048, Cfg::BOX_BYTES, 1024);
+                    umma_f16(tmem_base + Cfg::O_COL, a_desc, b_desc, idesc_o, (i > 0 || kk > 0) ? 1u : 0u);
+                }
+                umma_commit(v_empty(s));
+                umma_commit(pv_done);
+                return true;
+            };
+            for (int i = 0; ok && i < n_tiles; ++i) {
+                const int s = i & 1;
+                const uint32_t ph = (i >> 1) & 1;
+                if (!mbar_wait(k_full(s), ph) || !mbar_wait(s_empty(s), ph ^ 1u)) {
+                    fa_report(p.status, 1, i);
+                    ok = false;
+                    break;
+                }
+                tc_fence_after_sync();
+                const uint32_t s_tmem = tmem_base + (s ? Cfg::S_COL1 : Cfg::S_COL0);
+#pragma unroll
+                for (int kk = 0; kk < D / 16; ++kk) {
+                    const uint32_t off = (kk >> 2) * Cfg::BOX_BYTES + (kk & 3) * 32;
+                    const uint64_t a_desc = make_smem_desc_sw128(q_smem + off, 16, 1024);
+                    const uint64_t b_desc = make_smem_desc_sw128(k_smem(s) + off, 16, 1024);
+                    umma_f16(s_tmem, a_desc, b_desc, idesc_s, kk > 0 ? 1u : 0u);
+                }
+                umma_commit(k_empty(s));
+                umma_commit(s_full(s));
+                if (i > 0) ok = issue_pv(i - 1);
+            }
+            if (ok && n_tiles > 0) issue_pv(n_tiles - 1);
+        }
+    } else {
+        // ------------------------------------------------------------ softmax warps (2..5)
+        const int quad = warp & 3;
+        const int row = quad * 32 + lane;
+        const int q = q0 + row;
+        const uint32_t lane_addr = static_cast<uint32_t>(quad * 32) << 16;
+        const float sl2 = p.scale_log2;
+        float m_run = -INFINITY;  // running max of scale*log2e*s
+        float l_run = 0.f;        // running sum of exp2(scale*log2e*s - m_run)
+        bool ok = true;
+        for (int i = 0; ok && i < n_tiles; ++i) {
+            const int s = i & 1;
+            const uint32_t ph = (i >> 1) & 1;
+            if (!mbar_wait(s_full(s), ph)) {
+                fa_report(p.status, 2, i);
+                ok = false;
+                break;
+            }
+            tc_fence_after_sync();
+            const uint32_t s_addr = tmem_base + (s ? Cfg::S_COL1 : Cfg::S_COL0) + lane_addr;
+            const int kv0 = i * FA_BN;
+            const bool need_mask = (p.causal && kv0 + FA_BN - 1 > q0) || (kv0 + FA_BN > p.S);
+            const int col_limit = p.causal ? min(p.S - 1, q) : p.S - 1;  // last visible key
+
+            // pass 1: row maximum
+            float mx = -INFINITY;
+#pragma unroll 1
+            for (int c = 0; c < FA_BN / 32; ++c) {
+                uint32_t v[32];
+                tmem_ld_32x32b_x32(s_addr + c * 32, v);
+                tmem_wait_ld();
+#pragma unroll
+                for (int j = 0; j < 32; ++j) {
+                    float x = __uint_as_float(v[j]) * sl2;
+                    if (need_mask && kv0 + c * 32 + j > col_limit) x = -INFINITY;
+                    mx = fmaxf(mx, x);
+                }
+            }
+            const float m_new = fmaxf(m_run, mx);
+            const float m_safe = (m_new == -INFINITY) ? 0.f : m_new;
+            const float alpha = fast_exp2(m_run - m_safe);
+
+            // pass 2: probabilities -> fp16 P tile (K-major, 128-byte swizzle), row sum
+            float sum = 0.f;
+            const uint32_t p_base = p_smem(s);
+#pragma unroll 1
+            for (int c = 0; c < FA_BN / 32; ++c) {
+                uint32_t v[32];
+                tmem_ld_32x32b_x32(s_addr + c * 32, v);
+                tmem_wait_ld();
+                float e[32];
+#pragma unroll
+                for (int j = 0; j < 32; ++j) {
+                    float x = fmaf(__uint_as_float(v[j]), sl2, -m_safe);
+                    if (need_mask && kv0 + c * 32 + j > col_limit) x = -INFINITY;
+                    e[j] = fast_exp2(x);
+                    sum += e[j];
+                }
+#pragma unroll
+                for (int g = 0; g < 4; ++g) {
+                    const int col = c * 32 + g * 8;  // key index inside the tile
+                    const uint32_t dst = p_base + (col >> 6) * Cfg::BOX_BYTES + sw128_offset(row, (col & 63) >> 3);
+                    asm volatile("st.shared.v4.u32 [%0], {%1, %2, %3, %4};" ::"r"(dst),
+                                 "r"(pack_half2(e[g * 8 + 0], e[g * 8 + 1])), "r"(pack_half2(e[g * 8 + 2], e[g * 8 + 3])),
+                                 "r"(pack_half2(e[g * 8 + 4], e[g * 8 + 5])), "r"(pack_half2(e[g * 8 + 6], e[g * 8 + 7]))
+                                 : "memory");
+                }
+            }
+            tc_fence_before_sync();
+            mbar_arrive(s_empty(s));
+            l_run = l_run * alpha + sum;
+            m_run = m_new;
+
+            if (i > 0) {
+                // O holds the sum through tile i-1; bring it to the new maximum before P_i V_i
+                if (!mbar_wait(pv_done, (i - 1) & 1)) {
+                    fa_report(p.status, 2, 1000 + i);
+                    ok = false;
+                    break;
+                }
+                tc_fence_after_sync();
+                if (__any_sync(0xffffffffu, alpha != 1.f)) {
+                    const uint32_t o_addr = tmem_base + Cfg::O_COL + lane_addr;
+#pragma unroll 1
+                    for (int c = 0; c < D / 32; ++c) {
+                        uint32_t v[32];
+                        tmem_ld_32x32b_x32(o_addr + c * 32, v);
+                        tmem_wait_ld();
+#pragma unroll
+                        for (int j = 0; j < 32; ++j) v[j] = __float_as_uint(__uint_as_float(v[j]) * alpha);
+                        tmem_st_32x32b_x32(o_addr + c * 32, v);
+                    }
+                    tmem_wait_st();
+                }
+            }
+            fence_proxy_async_smem();
+            tc_fence_before_sync();
+            mbar_arrive(p_ready(s));
+        }
+        if (ok) {
+            if (!mbar_wait(pv_done, (n_tiles - 1) & 1)) {
+                fa_report(p.status, 2, -1);
+            } else {
+                tc_fence_after_sync();
+                const float inv = (l_run > 0.f) ? 1.f / l_run : 0.f;
+                const uint32_t o_addr = tmem_base + Cfg::O_COL + lane_addr;
+                __half* out = p.O + (static_cast<size_t>(bh) * p.S + q) * D;
+#pragma unroll 1
+                for (int c = 0; c < D / 32; ++c) {
+                    uint32_t v[32];
+                    tmem_ld_32x32b_x32(o_addr + c * 32, v);
+                    tmem_wait_ld();
+                    if (q < p.S) {
+#pragma unroll
+                        for (int g = 0; g < 4; ++g) {
+                            uint4 o;
+                            o.x = pack_half2(__uint_as_float(v[g * 8 + 0]) * inv, __uint_as_float(v[g * 8 + 1]) * inv);
+                            o.y = pack_half2(__uint_as_float(v[g * 8 + 2]) * inv, __uint_as_float(v[g * 8 + 3]) * inv);
+                            o.z = pack_half2(__uint_as_float(v[g * 8 + 4]) * inv, __uint_as_float(v[g * 8 + 5]) * inv);
+                            o.w = pack_half2(__uint_as_float(v[g * 8 + 6]) * inv, __uint_as_float(v[g * 8 + 7]) * inv);
+                            *reinterpret_cast<uint4*>(out + c * 32 + g * 8) = o;
+                        }
+                    }
+                }
+            }
+        }
+    }
+
+    tc_fence_before_sync();
+    __syncthreads();
+    if (warp == 1) {
+        tc_fence_after_sync();
+        tmem_dealloc(tmem_base, Cfg::TMEM_COLS);
+    }
+}
+
+template <int D>
+static int launch_fmha(const void* Q, const void* K, const void* V, const FaParams& p, cudaStream_t stream) {
+    using Cfg = FaCfg<D>;
+    static bool attr_set[64] = {};
+    int dev = 0;
+    WB_CHECK_CUDA(cudaGetDevice(&dev));
+    if (dev >= 0 && dev < 64 && !attr_set[dev]) {
+        WB_CHECK_CUDA(cudaFuncSetAttribute(fmha_fwd_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                           Cfg::SMEM_BYTES));
+        attr_set[dev] = true;
+    }
+    CUtensorMap tq, tk, tv;
+    const uint64_t dims[3] = {static_cast<uint64_t>(D), static_cast<uint64_t>(p.S),
+                              static_cast<uint64_t>(p.B) * p.H};
+    const uint64_t strides[3] = {0, static_cast<uint64_t>(D) * 2, static_cast<uint64_t>(p.S) * D * 2};
+    const uint32_t box[3] = {64, 128, 1};
+    int rc = encode_tmap(&tq, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 3, Q, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_128B);
+    if (rc != WMMA_OPS_OK) return rc;
+    rc = encode_tmap(&tk, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 3, K, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_128B);
+    if (rc != WMMA_OPS_OK) return rc;
+    rc = encode_tmap(&tv, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 3, V, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_128B);
+    if (rc != WMMA_OPS_OK) return rc;
+    dim3 grid((p.S + FA_BM - 1) / FA_BM, p.B * p.H);
+    fmha_fwd_kernel<D><<<grid, FA_THREADS, Cfg::SMEM_BYTES, stream>>>(tq, tk, tv, p);
+    WB_CHECK_CUDA(cudaGetLastError());
+    return WMMA_OPS_OK;
+}
+
+}  // namespace wb
+
+extern "C" int wmma_ops_fmha_fwd(const void* Q, const void* K, const void* V, void* O, int B, int H, int S,
+                                 int D, float scale, int causal, int* status, void* stream) {
+    using namespace wb;
+    WB_REQUIRE(B >= 0 && H >= 0 && S >= 0, WMMA_OPS_ERR_INVALID, "flash_attention: negative dimension");
+    WB_REQUIRE(D == 64 || D == 128, WMMA_OPS_ERR_INVALID, "flash_attention: head dimension must be 64 or 128 (got %d)", D);
+    if (B == 0 || H == 0 || S == 0) return WMMA_OPS_OK;
+    WB_REQUIRE(Q != nullptr && K != nullptr && V != nullptr && O != nullptr, WMMA_OPS_ERR_INVALID,
+               "flash_attention: null pointer");
+    WB_REQUIRE(static_cast<long long>(B) * H <= 65535, WMMA_OPS_ERR_INVALID,
+               "flash_attention: B*H must not exceed 65535 (got %lld)", static_cast<long long>(B) * H);
+    for (const void* ptr : {Q, K, V, static_cast<const void*>(O)})
+        WB_REQUIRE(reinterpret_cast<uintptr_t>(ptr) % 16 == 0, WMMA_OPS_ERR_INVALID,
+                   "flash_attention: tensors must be 16-byte aligned");
+    FaParams p;
+    p.O = static_cast<__half*>(O);
+    p.B = B;
+    p.H = H;
+    p.S = S;
+    p.D = D;
+    if (scale < 0.f) scale = 1.0f / sqrtf(static_cast<float>(D));
+    p.scale_log2 = scale * 1.4426950408889634f;
+    p.causal = causal ? 1 : 0;
+    p.status = status;
+    if (D == 128) return launch_fmha<128>(Q, K, V, p, static_cast<cudaStream_t>(stream));
+    return launch_fmha<64>(Q, K, V, p, static_cast<cudaStream_t>(stream));
+}
