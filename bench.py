@@ -195,6 +195,105 @@ def run_reference_arm(args):
     }))
 
 
+# ----------------------------------------------------------------------------- other north-star figures
+def _time_calls(fns, iters, world, dev):
+    """ms per call, cycling through `fns` (distinct buffers defeat the L2 for HBM-bound rows)."""
+    for f in fns:
+        f()
+    barrier_sync(world)
+    e0 = torch.cuda.Event(enable_timing=True)
+    e1 = torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(iters):
+        for f in fns:
+            f()
+    e1.record()
+    barrier_sync(world)
+    return max_over_ranks(e0.elapsed_time(e1), world, dev) / (iters * len(fns))
+
+
+def measure_w4a16(w, dev, peaks, world):
+    """W4A16 GEMM, K=4096, N=11008, group 128, M in {1,16,128,4096}: GB/s of algorithmic bytes and
+    TFLOP/s. Eight distinct weight sets (8 x 23 MB > L2) are cycled so decode rows read HBM."""
+    from oracle import int4
+    K, N, g = 4096, 11008, 128
+    nbuf = 8
+    gen = torch.Generator(device=dev).manual_seed(77)
+    weights = []
+    for _ in range(nbuf):
+        codes = torch.randint(0, 16, (K, N), generator=gen, device=dev, dtype=torch.uint8)
+        scales = (torch.rand(K // g, N, generator=gen, device=dev) * 0.019 + 0.001).half()
+        weights.append(w.int4_prepack(codes, scales, g))
+        del codes
+    rows = {}
+    for M in (1, 16, 128, 4096):
+        A = torch.randn(M, K, generator=gen, device=dev).half()
+        fns = [(lambda q=q, sc=sc: w.matmul_w4a16(A, q, sc, g)) for q, sc in weights]
+        ms = _time_calls(fns, 3 if M > 128 else 10, world, dev)
+        by = int4.w4a16_bytes(M, N, K, g)
+        gbs, tf = by / ms / 1e6, 2.0 * M * N * K / ms / 1e9
+        rows[f"M{M}"] = {"us": ms * 1e3, "gbs": gbs, "tflops": tf, "hbm_frac": gbs / peaks["hbm_gbs"],
+                         "tensor_frac": tf / peaks["tflops"]}
+    return rows
+
+
+def measure_fmha(w, dev, peaks, world):
+    from oracle import attention as oa
+    rows = {}
+    gen = torch.Generator(device=dev).manual_seed(78)
+    for S in (1024, 2048, 4096):
+        Q = torch.randn(4, 32, S, 128, generator=gen, device=dev).half()
+        Kt = torch.randn(4, 32, S, 128, generator=gen, device=dev).half()
+        V = torch.randn(4, 32, S, 128, generator=gen, device=dev).half()
+        for causal in (False, True):
+            ms = _time_calls([lambda: w.flash_attention(Q, Kt, V, causal)], 5, world, dev)
+            tf = oa.fmha_flops(4, 32, S, 128, causal) / ms / 1e9
+            rows[f"S{S}_{'causal' if causal else 'full'}"] = {"ms": ms, "tflops": tf, "tensor_frac": tf / peaks["tflops"]}
+    return rows
+
+
+def measure_layer(w, dev, rank, world, steps):
+    """Llama-7B-shaped W4A16 linears on 8192 tokens, column/row sharded over `world` ranks with
+    an NCCL all-reduce after O and down (strong scaling: the 8192 tokens are fixed)."""
+    from oracle import layer as olayer
+    from wmma_ops_b200 import sharded
+    tokens = 8192
+    gen = torch.Generator(device=dev).manual_seed(99)   # same weights on every rank
+    shapes = {"qkv": (4096, 12288), "o": (4096, 4096), "gate_up": (4096, 22016), "down": (11008, 4096)}
+    full = {}
+    for name, (K, N) in shapes.items():
+        codes = torch.randint(0, 16, (K, N), generator=gen, device=dev, dtype=torch.uint8)
+        scales = (torch.rand(K // 128, N, generator=gen, device=dev) * 0.019 + 0.001).half()
+        full[name] = (codes, scales)
+    local = sharded.shard_layer_weights(full, rank, world)
+    del full
+    x = torch.randn(tokens, 4096, generator=gen, device=dev).half()
+    out = {}
+    for label, rdt, chunks in (("fp32_reduce", torch.float32, 1), ("fp16_reduce_chunked", torch.float16, 4)):
+        if world == 1 and label != "fp32_reduce":
+            continue
+        layer = sharded.ShardedDecoderLinears(local, world=world, reduce_dtype=rdt, chunks=chunks)
+        for _ in range(3):
+            layer(x)
+        ms = time_region(lambda: layer(x), max(3, min(steps, 10)), world, dev)
+        out[label] = {"ms": ms, "tflops": olayer.layer_flops(tokens) / ms / 1e9, "tokens_per_s": tokens / ms * 1e3}
+        del layer
+    best = max(out.values(), key=lambda r: r["tflops"])
+    return {"workload": "llama7b_linears_w4a16_8192_tokens", "scaling": "strong", "n_gpus": world,
+            "parallelism": f"tp{world}", "ms": best["ms"], "tflops": best["tflops"], "tokens_per_s": best["tokens_per_s"],
+            "variants": out}
+
+
+def extra_measurements(args, w, dev, rank, world, peaks):
+    out = {}
+    if world == 1:
+        out["w4a16"] = measure_w4a16(w, dev, peaks, world)
+        out["fmha"] = measure_fmha(w, dev, peaks, world)
+        torch.cuda.empty_cache()
+    out["layer"] = measure_layer(w, dev, rank, world, args.steps)
+    return out
+
+
 # ----------------------------------------------------------------------------- GPU arm
 def run_ours(args):
     import wmma_ops_b200 as w

@@ -1,0 +1,48 @@
+"""The sharded layer on one GPU: each rank's shard is computed in turn on the same device and the
+partial outputs are summed on the host side of the test (ranks that wait on one another are never
+run as separate launches on one GPU). Checks the kernels on shard shapes (1408/1280-column
+tiles, K = 1408) and the plan, against the single-process oracle."""
+import pytest
+import torch
+
+import wmma_ops_b200 as w
+from oracle import gemm as og
+from oracle import layer as olayer
+from wmma_ops_b200 import sharded
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.mark.parametrize("world", [1, 8])
+def test_layer_full_shapes_few_tokens(cuda, world):
+    weights = olayer.make_layer_weights(seed=21)
+    g = torch.Generator().manual_seed(5)
+    x = torch.randn(192, 4096, generator=g).to(torch.float16)
+    ref_attn, ref_mlp = olayer.layer_ref(x, weights)
+    xd = x.to(cuda)
+    layers = []
+    for r in range(world):
+        local = {k: (c.to(cuda), s.to(cuda)) for k, (c, s) in sharded.shard_layer_weights(weights, r, world).items()}
+        layers.append(sharded.ShardedDecoderLinears(local, world=1))
+    # emulate the two all-reduces by summing the ranks' partials
+    attn = None
+    for layer in layers:
+        qkv = layer._matmul(xd, "qkv")
+        part = layer._matmul(qkv[:, :layer.q_cols].half(), "o")
+        attn = part if attn is None else attn + part
+    mlp = None
+    h = attn.half()
+    for layer in layers:
+        gu = layer._matmul(h, "gate_up")
+        f = layer.ffn_local
+        act = (torch.nn.functional.silu(gu[:, :f]) * gu[:, f:]).half()
+        part = layer._matmul(act, "down")
+        mlp = part if mlp is None else mlp + part
+    torch.cuda.synchronize()
+    w.check_status()
+    assert og.rel_frobenius(attn, ref_attn) < 1e-3
+    assert og.rel_frobenius(mlp, ref_mlp) < 2e-3
+    if world == 1:
+        a2, m2 = layers[0](xd)
+        torch.cuda.synchronize()
+        assert torch.equal(a2, attn) and torch.equal(m2, mlp)

@@ -1,0 +1,150 @@
+"""Column/row-sharded decoder-layer linears over 1/2/4/8 GPUs (one process per GPU).
+
+The reference is single-GPU; this is the layer-shaped workload built from its GEMM path:
+W4A16 projections QKV (hidden -> 3*hidden), O (hidden -> hidden), gate/up (hidden -> 2*ffn) and
+down (ffn -> hidden) on a block of tokens. QKV and gate/up are column-parallel (output columns
+sharded, no communication), O and down are row-parallel (K sharded) and end in the only
+collective of the project, an all-reduce (sum) of the partial outputs through
+torch.distributed (NCCL on GPUs).
+
+Sharding rules
+  * shard boundaries fall on multiples of 128 columns / rows, which are both the quantisation
+    group size and the kernel's column-tile width, so scales and packed blocks are never split;
+    11008 = 86 groups is cut as evenly as 86 allows (tp=4: 22,22,21,21; tp=8: 11 x6, 10 x2);
+  * the Q, K and V sections of the QKV weight are each cut by rank, so rank r's slice of the Q
+    section is exactly the K-shard of O it owns (no exchange between QKV and O);
+  * gate and up are cut with the same partition as down's rows, so silu(gate) * up is local.
+Every rank packs its own shard after slicing (the packed layout is tile-major along K).
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass
+from typing import Callable, Dict, List, Optional, Tuple
+
+import torch
+
+GROUP = 128
+
+
+def split_units(total_units: int, parts: int) -> List[Tuple[int, int]]:
+    """Cuts `total_units` into `parts` contiguous ranges as evenly as possible (the first
+    total_units % parts ranges get one more). Returns [(start, stop)] in units."""
+    if parts < 1 or total_units < parts:
+        raise ValueError(f"cannot cut {total_units} units into {parts} non-empty parts")
+    base, extra = divmod(total_units, parts)
+    out, start = [], 0
+    for r in range(parts):
+        n = base + (1 if r < extra else 0)
+        out.append((start, start + n))
+        start += n
+    return out
+
+
+def shard_range(size: int, rank: int, world: int, unit: int = GROUP) -> Tuple[int, int]:
+    """[start, stop) of rank's shard of a dimension of `size` cut on multiples of `unit`."""
+    if size % unit != 0:
+        raise ValueError(f"dimension {size} is not a multiple of {unit}")
+    a, b = split_units(size // unit, world)[rank]
+    return a * unit, b * unit
+
+
+@dataclass
+class LayerShapes:
+    hidden: int = 4096
+    qkv_out: int = 12288
+    ffn: int = 11008
+    group: int = GROUP
+
+
+def shard_layer_weights(weights: Dict[str, Tuple[torch.Tensor, torch.Tensor]], rank: int, world: int,
+                        shapes: LayerShapes = LayerShapes()) -> Dict[str, Tuple[torch.Tensor, torch.Tensor]]:
+    """Slices full (codes [K,N] uint8, scales [K/g,N] fp16) pairs into this rank's shards.
+    Pure tensor slicing; works on any device."""
+    g = shapes.group
+    h, f = shapes.hidden, shapes.ffn
+    sec = shapes.qkv_out // 3
+    out = {}
+
+    def cols(pair, ranges):
+        codes, scales = pair
+        return (torch.cat([codes[:, a:b] for a, b in ranges], dim=1).contiguous(),
+                torch.cat([scales[:, a:b] for a, b in ranges], dim=1).contiguous())
+
+    def rows(pair, a, b):
+        codes, scales = pair
+        return codes[a:b].contiguous(), scales[a // g:b // g].contiguous()
+
+    qa, qb = shard_range(sec, rank, world, g)
+    out["qkv"] = cols(weights["qkv"], [(s * sec + qa, s * sec + qb) for s in range(3)])
+    out["o"] = rows(weights["o"], qa, qb)
+    fa, fb = shard_range(f, rank, world, g)
+    out["gate_up"] = cols(weights["gate_up"], [(fa, fb), (f + fa, f + fb)])
+    out["down"] = rows(weights["down"], fa, fb)
+    return out
+
+
+class ShardedDecoderLinears:
+    """One rank's part of the layer. `matmul(x_fp16, name) -> fp32` computes x @ W_local[name];
+    by default it is the fused W4A16 kernel on prepacked shards. `all_reduce(t)` sums a tensor
+    over the ranks in place (torch.distributed by default; a no-op for world size 1)."""
+
+    def __init__(self, local_weights: Dict[str, Tuple[torch.Tensor, torch.Tensor]], world: int = 1,
+                 group: int = GROUP, matmul: Optional[Callable] = None, all_reduce: Optional[Callable] = None,
+                 reduce_dtype: torch.dtype = torch.float32, chunks: int = 1):
+        self.world = world
+        self.group = group
+        self.reduce_dtype = reduce_dtype
+        self.chunks = max(1, chunks)
+        self.q_cols = local_weights["qkv"][0].shape[1] // 3
+        self.ffn_local = local_weights["gate_up"][0].shape[1] // 2
+        if matmul is None:
+            from .quant import int4_prepack, matmul_w4a16
+            packed = {k: int4_prepack(c, s, group) for k, (c, s) in local_weights.items()}
+            matmul = lambda x, name: matmul_w4a16(x, packed[name][0], packed[name][1], group)  # noqa: E731
+            self.packed = packed
+        self._matmul = matmul
+        if all_reduce is None:
+            all_reduce = self._dist_all_reduce
+        self._all_reduce = all_reduce
+
+    def _dist_all_reduce(self, t: torch.Tensor, async_op: bool = False):
+        if self.world == 1:
+            return None
+        import torch.distributed as dist
+        return dist.all_reduce(t, op=dist.ReduceOp.SUM, async_op=async_op)
+
+    def _row_parallel(self, x: torch.Tensor, name: str) -> torch.Tensor:
+        """x @ W_local (K-sharded) summed over ranks. Token chunks let the all-reduce of one
+        chunk overlap the GEMM of the next (NCCL runs on its own stream)."""
+        T = x.shape[0]
+        if self.world == 1:
+            return self._matmul(x, name)
+        n_chunks = min(self.chunks, max(1, T // 256))
+        bounds = [(i * T // n_chunks, (i + 1) * T // n_chunks) for i in range(n_chunks)]
+        parts, handles = [], []
+        for a, b in bounds:
+            part = self._matmul(x[a:b], name)
+            if self.reduce_dtype != part.dtype:
+                part = part.to(self.reduce_dtype)
+            handles.append(self._all_reduce(part, True) if n_chunks > 1 else self._all_reduce(part))
+            parts.append(part)
+        for h in handles:
+            if h is not None and hasattr(h, "wait"):
+                h.wait()
+        return parts[0] if n_chunks == 1 else torch.cat(parts, dim=0)
+
+    def forward(self, x: torch.Tensor) -> Tuple[torch.Tensor, torch.Tensor]:
+        """x fp16 [T, hidden] (replicated) -> (attn_out, mlp_out), both [T, hidden], replicated,
+        in reduce_dtype. The glue is the oracle's: O's input is this rank's slice of the Q section
+        of the QKV output; the MLP input is attn_out; act = silu(gate) * up; fp16 between GEMMs."""
+        qkv = self._matmul(x, "qkv")
+        o_in = qkv[:, :self.q_cols].to(torch.float16)
+        attn_out = self._row_parallel(o_in, "o")
+        h = attn_out.to(torch.float16)
+        gu = self._matmul(h, "gate_up")
+        f = self.ffn_local
+        act = (torch.nn.functional.silu(gu[:, :f]) * gu[:, f:]).to(torch.float16)
+        mlp_out = self._row_parallel(act, "down")
+        return attn_out, mlp_out
+
+    __call__ = forward
