@@ -4,8 +4,9 @@ The reference has no multi-GPU code; the workload is the Llama-7B-shaped set of 
 projections on 8192 tokens: QKV 4096->12288, O 4096->4096, gate/up 4096->2x11008,
 down 11008->4096. The glue between the GEMMs is fixed here and used identically by the
 sharded implementation: O's input is the first 4096 columns of the QKV output (the attention
-core is outside this workload), the MLP input is the O output, act = silu(gate) * up, all
-intermediate activations are rounded to fp16.
+core is outside this workload), the MLP input is the O output, act = silu(gate) * up. Each
+intermediate is multiplied by GLUE_SCALE = 1/4 (exact in binary) before it is rounded to fp16, which
+keeps the random-weight activations of this synthetic layer inside fp16 range.
 """
 from __future__ import annotations
 
@@ -17,6 +18,7 @@ HIDDEN = 4096
 QKV_OUT = 12288
 FFN = 11008
 GROUP = 128
+GLUE_SCALE = 0.25
 
 
 def make_layer_weights(seed: int = 21, hidden: int = HIDDEN, qkv_out: int = QKV_OUT, ffn: int = FFN,
@@ -33,12 +35,12 @@ def layer_ref(x: torch.Tensor, weights, group: int = GROUP):
     """x fp16 [T, hidden] -> (attn_out fp32 [T, hidden], mlp_out fp32 [T, hidden])."""
     hidden = x.shape[1]
     qkv = int4.w4a16_ref(x, *weights["qkv"], group)
-    o_in = qkv[:, :hidden].to(torch.float16)
+    o_in = (qkv[:, :hidden] * GLUE_SCALE).to(torch.float16)
     attn_out = int4.w4a16_ref(o_in, *weights["o"], group)
-    h = attn_out.to(torch.float16)
+    h = (attn_out * GLUE_SCALE).to(torch.float16)
     gu = int4.w4a16_ref(h, *weights["gate_up"], group)
     ffn = gu.shape[1] // 2
-    act = (torch.nn.functional.silu(gu[:, :ffn]) * gu[:, ffn:]).to(torch.float16)
+    act = (torch.nn.functional.silu(gu[:, :ffn]) * gu[:, ffn:] * GLUE_SCALE).to(torch.float16)
     mlp_out = int4.w4a16_ref(act, *weights["down"], group)
     return attn_out, mlp_out
 

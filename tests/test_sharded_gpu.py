@@ -28,14 +28,14 @@ def test_layer_full_shapes_few_tokens(cuda, world):
     attn = None
     for layer in layers:
         qkv = layer._matmul(xd, "qkv")
-        part = layer._matmul(qkv[:, :layer.q_cols].half(), "o")
+        part = layer._matmul((qkv[:, :layer.q_cols] * sharded.GLUE_SCALE).half(), "o")
         attn = part if attn is None else attn + part
     mlp = None
-    h = attn.half()
+    h = (attn * sharded.GLUE_SCALE).half()
     for layer in layers:
         gu = layer._matmul(h, "gate_up")
         f = layer.ffn_local
-        act = (torch.nn.functional.silu(gu[:, :f]) * gu[:, f:]).half()
+        act = (torch.nn.functional.silu(gu[:, :f]) * gu[:, f:] * sharded.GLUE_SCALE).half()
         part = layer._matmul(act, "down")
         mlp = part if mlp is None else mlp + part
     torch.cuda.synchronize()

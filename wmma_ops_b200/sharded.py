@@ -24,6 +24,9 @@ from typing import Callable, Dict, List, Optional, Tuple
 import torch
 
 GROUP = 128
+# Every intermediate is scaled by 1/4 (exact) before its fp16 rounding so that the random-weight
+# activations of the synthetic layer stay inside fp16 range; the oracle uses the same constant.
+GLUE_SCALE = 0.25
 
 
 def split_units(total_units: int, parts: int) -> List[Tuple[int, int]]:
@@ -136,14 +139,14 @@ class ShardedDecoderLinears:
     def forward(self, x: torch.Tensor) -> Tuple[torch.Tensor, torch.Tensor]:
         """x fp16 [T, hidden] (replicated) -> (attn_out, mlp_out), both [T, hidden], replicated,
         in reduce_dtype. The glue is the oracle's: O's input is this rank's slice of the Q section
-        of the QKV output; the MLP input is attn_out; act = silu(gate) * up; fp16 between GEMMs."""
+        of the QKV output; the MLP input is attn_out; act = silu(gate) * up; each scaled by GLUE_SCALE, fp16 between GEMMs."""
         qkv = self._matmul(x, "qkv")
-        o_in = qkv[:, :self.q_cols].to(torch.float16)
+        o_in = (qkv[:, :self.q_cols] * GLUE_SCALE).to(torch.float16)
         attn_out = self._row_parallel(o_in, "o")
-        h = attn_out.to(torch.float16)
+        h = (attn_out * GLUE_SCALE).to(torch.float16)
         gu = self._matmul(h, "gate_up")
         f = self.ffn_local
-        act = (torch.nn.functional.silu(gu[:, :f]) * gu[:, f:]).to(torch.float16)
+        act = (torch.nn.functional.silu(gu[:, :f]) * gu[:, f:] * GLUE_SCALE).to(torch.float16)
         mlp_out = self._row_parallel(act, "down")
         return attn_out, mlp_out
 
