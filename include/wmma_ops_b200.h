@@ -73,6 +73,27 @@ int wmma_ops_gemm_f16f32(const void* A, const void* B, const void* C_in, void* C
                          int K, float alpha, float beta, int tile_cfg, int split_k, void* workspace,
                          size_t workspace_bytes, int* status, void* stream);
 
+/* Split-K GEMM that allocates nothing and needs no workspace argument. It has no counterpart
+ * in the reference. It is for callers that cannot call cudaMalloc where they need the product:
+ * code living inside another framework's memory pool, plugins that are handed only their input
+ * and output buffers, loops that must not risk the device-wide synchronisation an allocation
+ * can cause. Same arithmetic and arguments as wmma_ops_gemm_f16f32; the partial products go to
+ * a fixed 8 MiB array in device memory that belongs to the library (each GPU that loads the
+ * library holds it until the process exits; wmma_ops_gemm_static_scratch_bytes() returns its
+ * size). Limits and rules:
+ *   - split_k * M * N * 4 bytes must fit in the array, otherwise WMMA_OPS_ERR_WORKSPACE with a
+ *     message that names both sizes (with tile_cfg AUTO and split_k 0 the library's own choice
+ *     of split_k is what is checked);
+ *   - the first call on each device looks up the array's device address; make that call
+ *     before any stream capture begins on that device;
+ *   - every call on a device shares the one array: two calls whose kernels can overlap on the
+ *     GPU (different streams, no ordering between them) race on it. Calls on one stream are
+ *     safe. Nothing in the array has to be zero: each call overwrites every partial it reads. */
+size_t wmma_ops_gemm_static_scratch_bytes(void);
+int wmma_ops_gemm_f16f32_splitk_static(const void* A, const void* B, const void* C_in, void* C_out, int M,
+                                       int N, int K, float alpha, float beta, int tile_cfg, int split_k,
+                                       int* status, void* stream);
+
 /* INT4 weight prepack ("W4-B200-v1"; the reference snapshot has no INT4 code, so the
  * format is defined here and restated in oracle/int4.py):
  *   codes    [K,N] uint8, values 0..15 (weight k,n = (code - 8) * scale[k / group][n])

@@ -36,6 +36,9 @@ SIGNATURES = {
     "wmma_ops_gemm_workspace_bytes": (_c_size_t, [_c_int, _c_int, _c_int, _c_int]),
     "wmma_ops_gemm_f16f32": (_c_int, [_vp, _vp, _vp, _vp, _c_int, _c_int, _c_int, _c_float, _c_float,
                                       _c_int, _c_int, _vp, _c_size_t, _vp, _vp]),
+    "wmma_ops_gemm_static_scratch_bytes": (_c_size_t, []),
+    "wmma_ops_gemm_f16f32_splitk_static": (_c_int, [_vp, _vp, _vp, _vp, _c_int, _c_int, _c_int, _c_float, _c_float,
+                                                    _c_int, _c_int, _vp, _vp]),
     "wmma_ops_int4_prepack": (_c_int, [_vp, _vp, _c_int, _c_int, _vp]),
     "wmma_ops_int4_unpack": (_c_int, [_vp, _vp, _c_int, _c_int, _vp]),
     "wmma_ops_int4_dequant": (_c_int, [_vp, _vp, _vp, _c_int, _c_int, _c_int, _vp]),

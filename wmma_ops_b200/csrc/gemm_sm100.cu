@@ -16,6 +16,8 @@
 // Warp roles per CTA (192 threads): warp 0 = TMA producer, warp 1 = TMEM owner + MMA issuer,
 // warps 2..5 = epilogue (TMEM -> registers -> alpha*acc + beta*C_in -> global).
 // Two TMEM accumulators let the epilogue of one tile overlap the main loop of the next.
+#include <mutex>
+
 #include "host_common.cuh"
 #include "ptx.cuh"
 
@@ -491,4 +493,66 @@ extern "C" int wmma_ops_gemm_f16f32(const void* A, const void* B, const void* C_
     if (rc != WMMA_OPS_OK) return rc;
     if (split_k > 1) return launch_reduce(static_cast<const float*>(workspace), split_k);
     return WMMA_OPS_OK;
+}
+
+// ---------------------------------------------------------------------------------------------
+// Split-K GEMM for callers that cannot allocate device memory.
+//
+// Some hosts of this library may not call cudaMalloc at the point where they need a GEMM: code
+// that runs inside another framework's memory pool and must not go around it, plugins that are
+// only handed their input and output buffers, and real-time loops where an allocation (which
+// may synchronise the device) is not acceptable. The split-K path normally needs a caller-owned
+// workspace for its partial products; this entry point keeps that workspace inside the library
+// instead, in a fixed array in device memory that every GPU which loads the library holds until
+// the process exits.
+namespace wb {
+
+constexpr size_t STATIC_SCRATCH_BYTES = 8u << 20;  // 8 MiB = 32 slices of a 256 x 256 fp32 product
+static __device__ __align__(256) float g_splitk_scratch[STATIC_SCRATCH_BYTES / sizeof(float)];
+
+// The array's name is only a handle on the host; its device address is looked up once per
+// device (with that device current) and cached.
+static int static_scratch_ptr(float** out) {
+    static float* cached[64] = {};
+    static std::mutex mu;
+    int dev = 0;
+    WB_CHECK_CUDA(cudaGetDevice(&dev));
+    WB_REQUIRE(dev >= 0 && dev < 64, WMMA_OPS_ERR_INVALID, "device index %d out of range", dev);
+    std::lock_guard<std::mutex> lock(mu);
+    if (cached[dev] == nullptr) {
+        void* ptr = nullptr;
+        WB_CHECK_CUDA(cudaGetSymbolAddress(&ptr, g_splitk_scratch));
+        cached[dev] = static_cast<float*>(ptr);
+    }
+    *out = cached[dev];
+    return WMMA_OPS_OK;
+}
+
+}  // namespace wb
+
+extern "C" size_t wmma_ops_gemm_static_scratch_bytes(void) { return wb::STATIC_SCRATCH_BYTES; }
+
+extern "C" int wmma_ops_gemm_f16f32_splitk_static(const void* A, const void* B, const void* C_in, void* C_out,
+                                                  int M, int N, int K, float alpha, float beta, int tile_cfg,
+                                                  int split_k, int* status, void* stream) {
+    using namespace wb;
+    WB_REQUIRE(M >= 1 && N >= 1 && K >= 1, WMMA_OPS_ERR_INVALID,
+               "gemm_splitk_static: M, N, K must be positive (got %d, %d, %d)", M, N, K);
+    // Resolve the tile and slice count here, so that the size check below sees the final plan.
+    if (tile_cfg == WMMA_OPS_TILE_AUTO) {
+        int auto_split = 1;
+        select_tile_impl(M, N, K, 148, &tile_cfg, &auto_split);
+        if (split_k == 0) split_k = auto_split;
+    }
+    if (split_k < 1) split_k = 1;
+    const size_t need = wmma_ops_gemm_workspace_bytes(M, N, K, split_k);
+    WB_REQUIRE(need <= STATIC_SCRATCH_BYTES, WMMA_OPS_ERR_WORKSPACE,
+               "gemm_splitk_static: split_k=%d of a %d x %d product needs %zu bytes of partial sums, more than "
+               "the built-in scratch of %zu bytes; use wmma_ops_gemm_f16f32 with a workspace of your own",
+               split_k, M, N, need, STATIC_SCRATCH_BYTES);
+    float* scratch = nullptr;
+    int rc = static_scratch_ptr(&scratch);
+    if (rc != WMMA_OPS_OK) return rc;
+    return wmma_ops_gemm_f16f32(A, B, C_in, C_out, M, N, K, alpha, beta, tile_cfg, split_k, scratch,
+                                STATIC_SCRATCH_BYTES, status, stream);
 }
