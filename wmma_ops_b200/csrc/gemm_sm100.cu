@@ -267,6 +267,216 @@ gemm_f16f32_kernel(const __grid_constant__ CUtensorMap tmap_a,
     }
 }
 
+// ---------------------------------------------------------------------------------------------
+// CTA-pair kernel: two CTAs of one cluster share a 256 x 256 output tile. The leader issues
+// tcgen05.mma.cta_group::2 (M = 256: 128 rows per CTA); each CTA stages its own 128 rows of A and
+// its own 128 of the 256 B columns, so per SM the shared-memory traffic for B is halved
+// compared with the 1-CTA 128 x 256 tile. No TMA multicast: every CTA loads what it holds.
+// Barriers: the leader's full[] counts the bytes of both CTAs' loads (the peer's TMA reports to
+// the leader's barrier); the leader's MMA thread commits to empty[] and acc_full[] of both CTAs
+// (one commit per CTA); both CTAs' epilogue threads arrive on the leader's acc_empty[] (256).
+constexpr int PAIR_BN = 256;
+constexpr int PAIR_STAGES = 6;
+constexpr int PAIR_A_BYTES = BM * BK * 2;            // 16 KB: this CTA's 128 rows
+constexpr int PAIR_B_BYTES = 2 * BK * 64 * 2;        // 16 KB: this CTA's 128 columns (two boxes)
+constexpr int PAIR_STAGE_BYTES = PAIR_A_BYTES + PAIR_B_BYTES;
+constexpr int PAIR_SMEM_BYTES = PAIR_STAGES * PAIR_STAGE_BYTES + 1024 + 256;
+
+__device__ __forceinline__ void decode_pair_unit(const GemmParams& p, int unit, int& mb2, int& nb) {
+    // m fastest inside groups of 8 pair-rows (= 16 m-blocks), as in decode_unit
+    const int group_rows = RASTER_GROUP_M / 2;
+    const int group_span = group_rows * p.n_blocks;
+    const int g = unit / group_span;
+    const int first = g * group_rows;
+    const int rows = min(group_rows, p.m_blocks - first);
+    const int r = unit - g * group_span;
+    mb2 = first + r % rows;
+    nb = r / rows;
+}
+
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(GEMM_THREADS, 1)
+gemm_f16f32_pair_kernel(const __grid_constant__ CUtensorMap tmap_a,
+                        const __grid_constant__ CUtensorMap tmap_b, const GemmParams p) {
+    extern __shared__ uint8_t smem_raw[];
+    const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+    const uint32_t bar_base = smem_base + PAIR_STAGES * PAIR_STAGE_BYTES;
+    auto full_bar = [&](int s) { return bar_base + 8u * s; };
+    auto empty_bar = [&](int s) { return bar_base + 8u * (PAIR_STAGES + s); };
+    auto acc_full_bar = [&](int b) { return bar_base + 8u * (2 * PAIR_STAGES + b); };
+    auto acc_empty_bar = [&](int b) { return bar_base + 8u * (2 * PAIR_STAGES + 2 + b); };
+    const uint32_t tmem_slot = bar_base + 8u * (2 * PAIR_STAGES + 4);
+
+    const int warp = threadIdx.x >> 5;
+    const int lane = threadIdx.x & 31;
+    const uint32_t cta_rank = cluster_ctarank();  // 0 = leader
+    const int cluster_id = blockIdx.x >> 1;
+    const int num_clusters = gridDim.x >> 1;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < PAIR_STAGES; ++s) {
+            mbar_init(full_bar(s), 1);
+            mbar_init(empty_bar(s), 1);
+        }
+        for (int b = 0; b < 2; ++b) {
+            mbar_init(acc_full_bar(b), 1);
+            mbar_init(acc_empty_bar(b), 256);
+        }
+        fence_barrier_init();
+        fence_proxy_async_smem();
+        prefetch_tmap(&tmap_a);
+        prefetch_tmap(&tmap_b);
+    }
+    if (warp == 1) {
+        tmem_alloc_pair(tmem_slot, 512);
+        tmem_relinquish_pair();
+    }
+    tc_fence_before_sync();
+    __syncthreads();
+    cluster_sync();  // both CTAs' barriers exist before anything arrives on them remotely
+    tc_fence_after_sync();
+    uint32_t tmem_base;
+    asm volatile("ld.shared.u32 %0, [%1];" : "=r"(tmem_base) : "r"(tmem_slot) : "memory");
+
+    const int total_units = p.m_blocks * p.n_blocks;  // m_blocks counts 256-row pair blocks here
+
+    if (warp == 0) {
+        if (lane == 0) {
+            int stage = 0;
+            uint32_t phase = 0;
+            bool ok = true;
+            for (int unit = cluster_id; ok && unit < total_units; unit += num_clusters) {
+                int mb2, nb;
+                decode_pair_unit(p, unit, mb2, nb);
+                const int row0 = mb2 * 256 + static_cast<int>(cta_rank) * 128;
+                const int col0 = nb * PAIR_BN + static_cast<int>(cta_rank) * 128;
+                for (int kb = 0; kb < p.kb_total; ++kb) {
+                    if (!mbar_wait(empty_bar(stage), phase ^ 1u)) {
+                        report_timeout(p.status, 10, kb);
+                        ok = false;
+                        break;
+                    }
+                    const uint32_t a_dst = smem_base + stage * PAIR_STAGE_BYTES;
+                    const uint32_t b_dst = a_dst + PAIR_A_BYTES;
+                    if (cta_rank == 0) mbar_arrive_expect_tx(full_bar(stage), 2 * PAIR_STAGE_BYTES);
+                    const uint32_t leader_full = mapa(full_bar(stage), 0);
+                    tma_load_2d_pair(a_dst, &tmap_a, leader_full, kb * BK, row0);
+                    tma_load_2d_pair(b_dst, &tmap_b, leader_full, col0, kb * BK);
+                    tma_load_2d_pair(b_dst + BK * 64 * 2, &tmap_b, leader_full, col0 + 64, kb * BK);
+                    if (++stage == PAIR_STAGES) {
+                        stage = 0;
+                        phase ^= 1u;
+                    }
+                }
+            }
+        }
+    } else if (warp == 1) {
+        if (lane == 0 && cta_rank == 0) {
+            constexpr uint32_t idesc = make_idesc_f16_f32(256, PAIR_BN, false, true);
+            int stage = 0;
+            uint32_t phase = 0;
+            int acc = 0;
+            uint32_t acc_phase = 0;
+            bool ok = true;
+            for (int unit = cluster_id; ok && unit < total_units; unit += num_clusters) {
+                if (!mbar_wait(acc_empty_bar(acc), acc_phase ^ 1u)) {
+                    report_timeout(p.status, 11, -1);
+                    break;
+                }
+                tc_fence_after_sync();
+                const uint32_t d_tmem = tmem_base + acc * PAIR_BN;
+                for (int kb = 0; kb < p.kb_total; ++kb) {
+                    if (!mbar_wait(full_bar(stage), phase)) {
+                        report_timeout(p.status, 11, kb);
+                        ok = false;
+                        break;
+                    }
+                    tc_fence_after_sync();
+                    const uint32_t a_src = smem_base + stage * PAIR_STAGE_BYTES;
+                    const uint32_t b_src = a_src + PAIR_A_BYTES;
+#pragma unroll
+                    for (int kk = 0; kk < BK / 16; ++kk) {
+                        const uint64_t a_desc = make_smem_desc_sw128(a_src + kk * 32, 16, 1024);
+                        const uint64_t b_desc = make_smem_desc_sw128(b_src + kk * 2048, BK * 64 * 2, 1024);
+                        umma_f16_pair(d_tmem, a_desc, b_desc, idesc, (kb > 0 || kk > 0) ? 1u : 0u);
+                    }
+                    umma_commit_pair(empty_bar(stage));
+                    umma_commit_pair(mapa(empty_bar(stage), 1));
+                    if (++stage == PAIR_STAGES) {
+                        stage = 0;
+                        phase ^= 1u;
+                    }
+                }
+                if (!ok) break;
+                umma_commit_pair(acc_full_bar(acc));
+                umma_commit_pair(mapa(acc_full_bar(acc), 1));
+                acc ^= 1;
+                if (acc == 0) acc_phase ^= 1u;
+            }
+        }
+    } else {
+        const int quad = warp & 3;
+        const int row_in_tile = quad * 32 + lane;
+        int acc = 0;
+        uint32_t acc_phase = 0;
+        const bool use_cin = (p.beta != 0.0f) && (p.C_in != nullptr);
+        const float alpha = p.alpha, beta = p.beta;
+        for (int unit = cluster_id; unit < total_units; unit += num_clusters) {
+            int mb2, nb;
+            decode_pair_unit(p, unit, mb2, nb);
+            if (!mbar_wait(acc_full_bar(acc), acc_phase)) {
+                report_timeout(p.status, 12, unit);
+                break;
+            }
+            tc_fence_after_sync();
+            const int row = mb2 * 256 + static_cast<int>(cta_rank) * 128 + row_in_tile;
+            float* out_row = p.C_out + static_cast<size_t>(row) * p.N;
+            const float* in_row = use_cin ? p.C_in + static_cast<size_t>(row) * p.N : nullptr;
+            const uint32_t t_addr = tmem_base + acc * PAIR_BN + (static_cast<uint32_t>(quad * 32) << 16);
+#pragma unroll 1
+            for (int c = 0; c < PAIR_BN / 32; ++c) {
+                uint32_t r[32];
+                tmem_ld_32x32b_x32(t_addr + c * 32, r);
+                tmem_wait_ld();
+                if (row < p.M) {
+                    const int col0 = nb * PAIR_BN + c * 32;
+#pragma unroll
+                    for (int j = 0; j < 8; ++j) {
+                        const int col = col0 + j * 4;
+                        if (col < p.N) {
+                            float4 v;
+                            v.x = alpha * __uint_as_float(r[4 * j + 0]);
+                            v.y = alpha * __uint_as_float(r[4 * j + 1]);
+                            v.z = alpha * __uint_as_float(r[4 * j + 2]);
+                            v.w = alpha * __uint_as_float(r[4 * j + 3]);
+                            if (use_cin) {
+                                const float4 cin = *reinterpret_cast<const float4*>(in_row + col);
+                                v.x += beta * cin.x;
+                                v.y += beta * cin.y;
+                                v.z += beta * cin.z;
+                                v.w += beta * cin.w;
+                            }
+                            *reinterpret_cast<float4*>(out_row + col) = v;
+                        }
+                    }
+                }
+            }
+            tc_fence_before_sync();
+            if (cta_rank == 0) mbar_arrive(acc_empty_bar(acc));
+            else mbar_arrive_cluster(mapa(acc_empty_bar(acc), 0));
+            acc ^= 1;
+            if (acc == 0) acc_phase ^= 1u;
+        }
+    }
+
+    tc_fence_before_sync();
+    __syncthreads();
+    cluster_sync();  // the peer's shared memory and barriers stay alive until both are done
+    if (warp == 1) {
+        tc_fence_after_sync();
+        tmem_dealloc_pair(tmem_base, 512);
+    }
+}
+
 // out[i] = alpha * sum_{s ascending} partial[s][i] + beta * c_in[i]; the order of the
 // reference's reduce kernel (wmma_xor_swizzle.hpp:334-353). With split == 0 it writes
 // beta * c_in (the K == 0 product).
@@ -381,6 +591,25 @@ static int launch_gemm(const CUtensorMap& ta, const CUtensorMap& tb, const GemmP
     return WMMA_OPS_OK;
 }
 
+static int launch_gemm_pair(const CUtensorMap& ta, const CUtensorMap& tb, GemmParams p, int sms,
+                            cudaStream_t stream) {
+    static bool attr_set[64] = {};
+    int dev = 0;
+    WB_CHECK_CUDA(cudaGetDevice(&dev));
+    if (dev >= 0 && dev < 64 && !attr_set[dev]) {
+        WB_CHECK_CUDA(cudaFuncSetAttribute(gemm_f16f32_pair_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                           PAIR_SMEM_BYTES));
+        attr_set[dev] = true;
+    }
+    p.m_blocks = ceil_div(p.M, 256);
+    p.n_blocks = ceil_div(p.N, PAIR_BN);
+    const int units = p.m_blocks * p.n_blocks;
+    const int clusters = units < sms / 2 ? units : sms / 2;
+    gemm_f16f32_pair_kernel<<<2 * clusters, GEMM_THREADS, PAIR_SMEM_BYTES, stream>>>(ta, tb, p);
+    WB_CHECK_CUDA(cudaGetLastError());
+    return WMMA_OPS_OK;
+}
+
 }  // namespace wb
 
 extern "C" int wmma_ops_select_tile(int M, int N, int K, int num_sms, int* tile_cfg, int* split_k) {
@@ -485,6 +714,8 @@ extern "C" int wmma_ops_gemm_f16f32(const void* A, const void* B, const void* C_
                         CU_TENSOR_MAP_SWIZZLE_128B);
     if (rc != WMMA_OPS_OK) return rc;
 
+    if (tile_cfg == WMMA_OPS_TILE_256x256_PAIR && split_k == 1)
+        return launch_gemm_pair(ta, tb, p, sms, stream);
     switch (bn) {
         case 64: rc = launch_gemm<64>(ta, tb, p, sms, stream); break;
         case 128: rc = launch_gemm<128>(ta, tb, p, sms, stream); break;
