@@ -387,6 +387,9 @@ def run_kernel_only(args, w, dev, A, B):
     if args.kernel_only == "gemm":
         for _ in range(3):
             w.matmul_adaptive(A, B)
+    elif args.kernel_only == "gemm_pair":
+        for _ in range(3):
+            w.matmul_tiled(A, B, 3)
     else:
         raise SystemExit(f"unknown --kernel-only {args.kernel_only}")
     torch.cuda.synchronize()

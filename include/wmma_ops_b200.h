@@ -97,8 +97,10 @@ int wmma_ops_gemm_f16f32_splitk_static(const void* A, const void* B, const void*
 /* INT4 weight prepack ("W4-B200-v1"; the reference snapshot has no INT4 code, so the
  * format is defined here and restated in oracle/int4.py):
  *   codes    [K,N] uint8, values 0..15 (weight k,n = (code - 8) * scale[k / group][n])
- *   qweight  [N, K/8] uint32. Word (n, j) holds k = 8j .. 8j+7 of column n; nibble p
- *            (bits 4p..4p+3) holds k = 8j + {0,2,4,6,1,3,5,7}[p].
+ *   qweight  uint32 [K/64][ceil(N/128)][128][8]. Block (kb, nt) is 4 KB: for the 128 columns
+ *            n = 128 nt + r (zero codes where n >= N) the codes k = 64 kb .. 64 kb + 63 as 8
+ *            words per column; word j, nibble p (bits 4p..4p+3) holds
+ *            k = 64 kb + 8 j + {0,2,4,6,1,3,5,7}[p].
  * Requirements: K % 64 == 0, N % 8 == 0. */
 int wmma_ops_int4_prepack(const void* codes_u8, void* qweight, int K, int N, void* stream);
 

@@ -7,13 +7,13 @@ unpack and dequant kernels must match bit for bit.
 Format
   codes    uint8 [K, N], values 0..15; weight[k, n] = (code[k, n] - 8) * scale[k // g, n]
   scales   fp16 [K // g, N] (g = group size along K, 128 in the configs)
-  qweight  uint32 [ceil(N/128), K // 64, 128, 8]: block (nt, kb) is 4 KB and holds, for the 128
+  qweight  uint32 [K // 64, ceil(N/128), 128, 8]: block (kb, nt) is 4 KB and holds, for the 128
            columns n = 128 nt + r (zero codes where n >= N), the codes k = 64 kb .. 64 kb + 63 as
            8 words per column; word j, nibble p (bits 4p .. 4p+3) holds
            k = 64 kb + 8 j + NIBBLE_K[p], NIBBLE_K = (0, 2, 4, 6, 1, 3, 5, 7).
            With this nibble order `(word >> 4i) & 0x000F000F` yields the adjacent pair
            (k = 8j+2i, 8j+2i+1) in the low / high half-word, which is what a half2 dequant wants;
-           with this block order one column tile is a contiguous run of 4 KB blocks along K.
+           blocks are ordered k-block major, so CTAs that walk K in step read one contiguous window.
 """
 from __future__ import annotations
 
@@ -25,15 +25,15 @@ ZERO_POINT = 8
 
 
 def pack_ref(codes: torch.Tensor) -> torch.Tensor:
-    """codes uint8 [K,N] -> qweight int32 [ceil(N/128), K//64, 128, 8] (bit pattern of uint32 words)."""
+    """codes uint8 [K,N] -> qweight int32 [K//64, ceil(N/128), 128, 8] (bit pattern of uint32 words)."""
     c = codes.detach().cpu().numpy().astype(np.uint32)
     K, N = c.shape
     assert K % 64 == 0 and c.max(initial=0) <= 15
     n_pad = -(-N // 128) * 128
     cp = np.zeros((K, n_pad), dtype=np.uint32)
     cp[:, :N] = c
-    # [kb, j, kk, nt, r] -> [nt, kb, r, j, kk]
-    t = cp.reshape(K // 64, 8, 8, n_pad // 128, 128).transpose(3, 0, 4, 1, 2)
+    # [kb, j, kk, nt, r] -> [kb, nt, r, j, kk]
+    t = cp.reshape(K // 64, 8, 8, n_pad // 128, 128).transpose(0, 3, 4, 1, 2)
     words = np.zeros(t.shape[:4], dtype=np.uint32)
     for p, kk in enumerate(NIBBLE_K):
         words |= t[..., kk] << np.uint32(4 * p)
@@ -41,14 +41,14 @@ def pack_ref(codes: torch.Tensor) -> torch.Tensor:
 
 
 def unpack_ref(qweight: torch.Tensor, K: int, N: int) -> torch.Tensor:
-    """qweight int32 [ceil(N/128), K//64, 128, 8] -> codes uint8 [K,N]."""
+    """qweight int32 [K//64, ceil(N/128), 128, 8] -> codes uint8 [K,N]."""
     n_tiles = -(-N // 128)
-    w = qweight.detach().cpu().numpy().view(np.uint32).reshape(n_tiles, K // 64, 128, 8)
-    t = np.zeros((n_tiles, K // 64, 128, 8, 8), dtype=np.uint8)
+    w = qweight.detach().cpu().numpy().view(np.uint32).reshape(K // 64, n_tiles, 128, 8)
+    t = np.zeros((K // 64, n_tiles, 128, 8, 8), dtype=np.uint8)
     for p, kk in enumerate(NIBBLE_K):
         t[..., kk] = ((w >> np.uint32(4 * p)) & np.uint32(0xF)).astype(np.uint8)
-    # [nt, kb, r, j, kk] -> [kb, j, kk, nt, r]
-    c = t.transpose(1, 3, 4, 0, 2).reshape(K, n_tiles * 128)
+    # [kb, nt, r, j, kk] -> [kb, j, kk, nt, r]
+    c = t.transpose(0, 3, 4, 1, 2).reshape(K, n_tiles * 128)
     return torch.from_numpy(np.ascontiguousarray(c[:, :N]))
 
 

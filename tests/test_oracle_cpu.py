@@ -93,7 +93,7 @@ def test_int4_nibble_order_by_hand():
     codes = torch.zeros(64, 8, dtype=torch.uint8)
     codes[8:16, 3] = torch.tensor([1, 2, 3, 4, 5, 6, 7, 9], dtype=torch.uint8)
     q = int4.pack_ref(codes)
-    assert q.shape == (1, 1, 128, 8)
+    assert q.shape == (1, 1, 128, 8)  # [K/64, ceil(N/128), 128, 8]
     # column 3, word 1 (k = 8..15): nibbles p=0..7 hold k = 8+{0,2,4,6,1,3,5,7} -> 1,3,5,7,2,4,6,9
     assert (q[0, 0, 3, 1].item() & 0xFFFFFFFF) == 0x96427531
     assert int(q.abs().sum()) == abs(q[0, 0, 3, 1].item())

@@ -6,7 +6,7 @@
 // (rocwmma_patch/rocwmma_gfx1151.hpp:43-281: fragment<>, load_matrix_sync_lds*, mma_sync,
 // store_matrix_sync) and its LDS staging helpers (wmma_device_helpers.hpp:20-172).
 //
-// Every wait in here is bounded: a wait that does not complete within WAIT_LIMIT_NS
+// Every wait in here is bounded: a wait that does not complete within WAIT_LIMIT_CYCLES
 // returns false, the caller records an error code in the launch's status word and
 // leaves its loop, so a protocol bug ends the kernel instead of hanging the GPU.
 #pragma once
@@ -16,7 +16,7 @@
 
 namespace wb {
 
-constexpr unsigned long long WAIT_LIMIT_NS = 2000000000ull;  // 2 s per wait
+constexpr long long WAIT_LIMIT_CYCLES = 4000000000ll;  // about 2 s of SM clocks per wait
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) {
     return static_cast<uint32_t>(__cvta_generic_to_shared(p));
@@ -88,13 +88,29 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
     return ok != 0;
 }
 
-// Bounded wait. Returns false when the phase did not complete in WAIT_LIMIT_NS.
+// Bounded wait. Returns false when the phase did not complete within WAIT_LIMIT_CYCLES.
+// The limit is counted on the SM's cycle counter: reading %globaltimer on the wait path cost
+// a few hundred nanoseconds per wait and paced whole pipelines.
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity) {
     if (mbar_try_wait(bar, parity)) return true;
-    const unsigned long long t0 = globaltimer_ns();
+    const long long t0 = clock64();
     uint32_t spins = 0;
     while (!mbar_try_wait(bar, parity)) {
-        if ((++spins & 0xff) == 0 && globaltimer_ns() - t0 > WAIT_LIMIT_NS) return false;
+        if ((++spins & 0xfff) == 0 && clock64() - t0 > WAIT_LIMIT_CYCLES) return false;
+    }
+    return true;
+}
+
+// Bounded wait for roles that are idle for long stretches (an epilogue warp waiting for a whole
+// tile, a producer waiting for a free slot): sleeps between polls so that it does not take
+// issue slots from the warps doing the work.
+__device__ __forceinline__ bool mbar_wait_relaxed(uint32_t bar, uint32_t parity, uint32_t sleep_ns = 128) {
+    if (mbar_try_wait(bar, parity)) return true;
+    const long long t0 = clock64();
+    uint32_t spins = 0;
+    while (!mbar_try_wait(bar, parity)) {
+        __nanosleep(sleep_ns);
+        if ((++spins & 0xff) == 0 && clock64() - t0 > WAIT_LIMIT_CYCLES) return false;
     }
     return true;
 }

@@ -4,10 +4,12 @@
 // arithmetic  C[M,N] = A[M,K] . ((code - 8) * scale[k / group][n])  are specified here and
 // restated on the CPU in oracle/int4.py.
 //
-// Packed format: uint32 [N_pad/128][K/64][128][8].  Block (nt, kb) is 4 KB and holds, for the
+// Packed format: uint32 [K/64][N_pad/128][128][8].  Block (kb, nt) is 4 KB and holds, for the
 // 128 weight columns n = 128 nt + r, the 64 codes k = 64 kb .. 64 kb + 63 as 8 words per
-// column; word j, nibble p holds k = 64 kb + 8 j + {0,2,4,6,1,3,5,7}[p].  A CTA streams the
-// blocks of one column tile as contiguous 4 KB bulk copies, so HBM sees long sequential reads.
+// column; word j, nibble p holds k = 64 kb + 8 j + {0,2,4,6,1,3,5,7}[p].  Blocks are ordered
+// k-block major: the CTAs of a launch walk K in step, so at any moment the whole GPU reads one
+// contiguous window of the weights and the requests spread over every memory channel (with
+// column-tile-major order the CTAs' streams sat 256 KB apart and camped on a few channels).
 //
 // Kernel: the weights sit on the 128-row side of the MMA (it computes C^T = W^T . A^T):
 //   A operand  = dequantised W^T tile, 128 columns-of-W x 64 k, fp16, K-major, 128-byte swizzle,
@@ -16,8 +18,8 @@
 //   accumulator = 128 TMEM lanes (weight columns) x BT columns (tokens), fp32.
 // One weight element is dequantised once per 256 tokens, so the same kernel serves decode
 // (M = 1..16, HBM-bound) and prefill (M in the thousands, tensor-bound).
-// Warps: 0 raw-weight producer, 1 activation producer, 2 MMA issuer + TMEM owner, 3 idle,
-// 4..11 dequant (each expands every eighth 4 KB block), 12..15 epilogue.  Split-K partials are combined by the last CTA to finish a
+// Warps: 2 MMA issuer + TMEM owner; 4..11 workers (each requests, expands and hands over whole
+// 4 KB blocks); 12..15 epilogue; 0, 1, 3 idle.  Split-K partials are combined by the last CTA to finish a
 // tile (arrival counter, no waiting), summed in ascending slice order.
 #include "host_common.cuh"
 #include "ptx.cuh"
@@ -27,23 +29,29 @@ namespace wb {
 constexpr int W4_TILE_N = 128;     // weight columns per CTA tile (MMA M)
 constexpr int W4_BK = 64;          // k per pipeline step
 constexpr int W4_RAW_BYTES = 4096; // one packed block
+constexpr int W4_SLOT_BYTES = W4_RAW_BYTES + W4_TILE_N * 2;  // + the block's 128 fp16 scales
 constexpr int W4_WT_BYTES = W4_TILE_N * W4_BK * 2;
 constexpr int W4_THREADS = 512;
 constexpr int W4_DQ_WARPS = 8;     // each dequant warp expands a whole 4 KB block; 8 blocks in flight
 
-template <int BT>
+template <int BT, bool WM>
 struct W4Cfg {
     static constexpr int X_BYTES = BT * W4_BK * 2;
     static constexpr int S_STAGE = W4_WT_BYTES + X_BYTES;
     // Wt + X ring. One dequant warp owns each stage (DQ = S), and the raw ring is a multiple
     // of S, so every barrier is waited on by the same warp pass after pass: a parity wait can
     // then never be more than one phase away from the barrier's state.
-    static constexpr int S = (BT >= 256) ? 4 : (BT >= 128) ? 6 : 8;
-    static constexpr int R = (BT >= 256) ? 8 : (BT >= 128) ? 6 : (BT >= 32) ? 8 : 16;
+    static constexpr int S = (BT >= 256) ? 4 : (BT >= 64) ? 6 : 8;
+    static constexpr int R = (BT >= 256) ? 4 : (BT >= 128) ? 6 : (BT >= 64) ? 12 : (BT >= 32) ? 8 : 16;
+    static_assert(S * S_STAGE + R * W4_SLOT_BYTES + 1024 + 512 <= 232448, "shared memory budget");
     static constexpr int DQ = S;
     static_assert(R % S == 0 && DQ <= W4_DQ_WARPS, "ring sizes must nest");
-    static constexpr int TMEM_COLS = (2 * BT < 32) ? 32 : 2 * BT;
-    static constexpr int SMEM_BYTES = S * S_STAGE + R * W4_RAW_BYTES + 1024 + 512;
+    // WM (worker-MMA, decode): every worker accumulates into its own BT columns, two sets
+    static constexpr int ACCS = WM ? DQ : 1;
+    static constexpr int TMEM_NEED = 2 * ACCS * BT;
+    static constexpr int TMEM_COLS = TMEM_NEED <= 32 ? 32 : TMEM_NEED <= 64 ? 64 : TMEM_NEED <= 128 ? 128 : TMEM_NEED <= 256 ? 256 : 512;
+    static_assert(TMEM_NEED <= 512, "TMEM budget");
+    static constexpr int SMEM_BYTES = S * S_STAGE + R * W4_SLOT_BYTES + 1024 + 512;
 };
 
 struct W4Params {
@@ -77,25 +85,25 @@ __device__ __forceinline__ void w4_decode(const W4Params& p, int unit, int& nt, 
     kb1 = static_cast<int>(static_cast<long long>(sl + 1) * p.kb_total / p.split);
 }
 
-// Position of a dequant warp in the CTA's sequence of k-block iterations.
+// Position of a worker warp in the CTA's sequence of k-block iterations.
 struct W4Cursor {
-    int unit, nt, kb, kb1;
+    int unit, nt, tt, kb, kb0, kb1;
     bool valid;
 };
 
 __device__ __forceinline__ void w4_cursor_start(const W4Params& p, int total_units, W4Cursor& c) {
     c.unit = blockIdx.x;
     c.valid = c.unit < total_units;
+    c.nt = c.tt = c.kb = c.kb0 = c.kb1 = 0;
     if (c.valid) {
-        int tt, sl, kb0;
-        w4_decode(p, c.unit, c.nt, tt, sl, kb0, c.kb1);
-        c.kb = kb0;
+        int sl;
+        w4_decode(p, c.unit, c.nt, c.tt, sl, c.kb0, c.kb1);
+        c.kb = c.kb0;
     }
 }
 
 // Moves the cursor `steps` iterations forward, crossing into later work units as needed.
-__device__ __forceinline__ void w4_cursor_advance(const W4Params& p, int total_units, W4Cursor& c,
-                                                  int steps) {
+__device__ __forceinline__ void w4_cursor_advance(const W4Params& p, int total_units, W4Cursor& c, int steps) {
     if (!c.valid) return;
     c.kb += steps;
     while (c.kb >= c.kb1) {
@@ -105,9 +113,9 @@ __device__ __forceinline__ void w4_cursor_advance(const W4Params& p, int total_u
             c.valid = false;
             return;
         }
-        int tt, sl, kb0;
-        w4_decode(p, c.unit, c.nt, tt, sl, kb0, c.kb1);
-        c.kb = kb0 + over;
+        int sl;
+        w4_decode(p, c.unit, c.nt, c.tt, sl, c.kb0, c.kb1);
+        c.kb = c.kb0 + over;
     }
 }
 
@@ -126,35 +134,22 @@ __device__ __forceinline__ void dq_word_store(uint32_t dst, uint32_t w, __half2 
     const uint32_t b = dq_pair((w >> 4) & 0x000F000Fu, scale2);
     const uint32_t c = dq_pair((w >> 8) & 0x000F000Fu, scale2);
     const uint32_t d = dq_pair((w >> 12) & 0x000F000Fu, scale2);
-    asm volatile("st.shared.v4.u32 [%0], {%1, %2, %3, %4};" ::"r"(dst), "r"(a), "r"(b), "r"(c), "r"(d)
-                 : "memory");
+    asm volatile("st.shared.v4.u32 [%0], {%1, %2, %3, %4};" ::"r"(dst), "r"(a), "r"(b), "r"(c), "r"(d));
 }
 
-// The eight scales one lane needs for a block: rows 16 q + lane / 2, q = 0..7.
-__device__ __forceinline__ void w4_load_scales(const W4Params& p, const W4Cursor& c, int lane,
-                                               __half (&sc)[8]) {
-    const int grp = c.kb / p.group_kb;
-    const __half* base = p.scales + static_cast<size_t>(grp) * p.N;
-#pragma unroll
-    for (int q = 0; q < 8; ++q) {
-        const int n = c.nt * W4_TILE_N + 16 * q + (lane >> 1);
-        sc[q] = (n < p.N) ? __ldg(base + n) : __ushort_as_half(0);
-    }
-}
-
-template <int BT>
+template <int BT, bool WM>
 __global__ void __launch_bounds__(W4_THREADS, 1)
-w4a16_gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const W4Params p) {
-    using Cfg = W4Cfg<BT>;
+w4a16_gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ CUtensorMap tmap_w,
+                  const __grid_constant__ CUtensorMap tmap_sc, const W4Params p) {
+    using Cfg = W4Cfg<BT, WM>;
     extern __shared__ uint8_t smem_raw_[];
     const uint32_t smem_base = (smem_u32(smem_raw_) + 1023u) & ~1023u;
     const uint32_t raw_base = smem_base + Cfg::S * Cfg::S_STAGE;
-    const uint32_t bar_base = raw_base + Cfg::R * W4_RAW_BYTES;
+    const uint32_t bar_base = raw_base + Cfg::R * W4_SLOT_BYTES;
     auto x_full = [&](int s) { return bar_base + 8u * s; };
     auto wt_full = [&](int s) { return bar_base + 8u * (Cfg::S + s); };
     auto st_empty = [&](int s) { return bar_base + 8u * (2 * Cfg::S + s); };
     auto raw_full = [&](int r) { return bar_base + 8u * (3 * Cfg::S + r); };
-    auto raw_empty = [&](int r) { return bar_base + 8u * (3 * Cfg::S + Cfg::R + r); };
     auto acc_full = [&](int b) { return bar_base + 8u * (3 * Cfg::S + 2 * Cfg::R + b); };
     auto acc_empty = [&](int b) { return bar_base + 8u * (3 * Cfg::S + 2 * Cfg::R + 2 + b); };
     const uint32_t tmem_slot = bar_base + 8u * (3 * Cfg::S + 2 * Cfg::R + 4);
@@ -172,15 +167,16 @@ w4a16_gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const W4Params p) 
         }
         for (int r = 0; r < Cfg::R; ++r) {
             mbar_init(raw_full(r), 1);
-            mbar_init(raw_empty(r), 1);
         }
         for (int b = 0; b < 2; ++b) {
-            mbar_init(acc_full(b), 1);
+            mbar_init(acc_full(b), WM ? Cfg::DQ : 1);
             mbar_init(acc_empty(b), 128);
         }
         fence_barrier_init();
         fence_proxy_async_smem();
         prefetch_tmap(&tmap_x);
+        prefetch_tmap(&tmap_w);
+        prefetch_tmap(&tmap_sc);
     }
     if (warp == 2) {
         tmem_alloc(tmem_slot, Cfg::TMEM_COLS);
@@ -194,60 +190,9 @@ w4a16_gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const W4Params p) 
 
     const int total_units = p.n_tiles * p.t_tiles * p.split;
 
-    if (warp == 0) {
-        // ------------------------------------------------ raw packed-weight producer
-        if (lane == 0) {
-            int r = 0;
-            uint32_t ph = 0;
-            bool ok = true;
-            for (int unit = blockIdx.x; ok && unit < total_units; unit += gridDim.x) {
-                int nt, tt, sl, kb0, kb1;
-                w4_decode(p, unit, nt, tt, sl, kb0, kb1);
-                const uint32_t* src =
-                    p.qweight + (static_cast<size_t>(nt) * p.kb_total + kb0) * (W4_RAW_BYTES / 4);
-                for (int kb = kb0; kb < kb1; ++kb, src += W4_RAW_BYTES / 4) {
-                    if (!mbar_wait(raw_empty(r), ph ^ 1u)) {
-                        w4_report(p.status, 0, kb);
-                        ok = false;
-                        break;
-                    }
-                    mbar_arrive_expect_tx(raw_full(r), W4_RAW_BYTES);
-                    bulk_load_1d(raw_base + r * W4_RAW_BYTES, src, W4_RAW_BYTES, raw_full(r));
-                    if (++r == Cfg::R) {
-                        r = 0;
-                        ph ^= 1u;
-                    }
-                }
-            }
-        }
-    } else if (warp == 1) {
-        // ------------------------------------------------ activation producer
-        if (lane == 0) {
-            int s = 0;
-            uint32_t ph = 0;
-            bool ok = true;
-            for (int unit = blockIdx.x; ok && unit < total_units; unit += gridDim.x) {
-                int nt, tt, sl, kb0, kb1;
-                w4_decode(p, unit, nt, tt, sl, kb0, kb1);
-                for (int kb = kb0; kb < kb1; ++kb) {
-                    if (!mbar_wait(st_empty(s), ph ^ 1u)) {
-                        w4_report(p.status, 1, kb);
-                        ok = false;
-                        break;
-                    }
-                    mbar_arrive_expect_tx(x_full(s), Cfg::X_BYTES);
-                    tma_load_2d(smem_base + s * Cfg::S_STAGE + W4_WT_BYTES, &tmap_x, x_full(s),
-                                kb * W4_BK, tt * BT);
-                    if (++s == Cfg::S) {
-                        s = 0;
-                        ph ^= 1u;
-                    }
-                }
-            }
-        }
-    } else if (warp == 2) {
+    if (warp == 2) {
         // ------------------------------------------------ MMA issuer
-        if (lane == 0) {
+        if (lane == 0 && !WM) {
             constexpr uint32_t idesc = make_idesc_f16_f32(W4_TILE_N, BT, false, false);
             int s = 0;
             uint32_t ph = 0;
@@ -295,62 +240,109 @@ w4a16_gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const W4Params p) 
         // Warp w (< DQ) expands iterations j = w, w + DQ, w + 2 DQ, ... of this CTA's k-block
         // sequence, a whole 4 KB block each, so DQ blocks are in flight and the fixed costs of
         // an iteration (two waits, a proxy fence, two arrivals) are paid once per block.
+        // Worker warps. Warp w (< DQ) owns pipeline stage w and handles iterations j = w, w + DQ,
+        // ... of this CTA's k-block sequence end to end: it waits for the packed block it
+        // requested earlier, requests the activation tile for its stage, expands the block,
+        // hands the stage to the MMA warp and requests the packed block of iteration j + R into
+        // the slot it has just emptied. There is no separate producer thread: a single thread
+        // issuing every TMA load of the CTA was starved by the workers' shared-memory traffic
+        // (about 350 ns per block), while eight warps issuing their own loads are not.
         const int w = warp - 4;
-        W4Cursor cur;
-        w4_cursor_start(p, total_units, cur);
-        w4_cursor_advance(p, total_units, cur, w);
-        if (w >= Cfg::DQ) cur.valid = false;
-        __half sc_cur[8], sc_next[8];
-        if (cur.valid) w4_load_scales(p, cur, lane, sc_cur);
-        for (int j = w; cur.valid; j += Cfg::DQ) {
-            // the scales of this warp's next block are requested now and used an iteration later
-            W4Cursor nxt = cur;
-            w4_cursor_advance(p, total_units, nxt, Cfg::DQ);
-            if (nxt.valid) w4_load_scales(p, nxt, lane, sc_next);
-
-            const int r = j % Cfg::R;
-            const int s = j % Cfg::S;
-            const uint32_t ph_r = (j / Cfg::R) & 1;
-            const uint32_t ph_s = (j / Cfg::S) & 1;
-            if (!mbar_wait(raw_full(r), ph_r)) {
-                w4_report(p.status, 3, j);
-                break;
+        if (w < Cfg::DQ) {
+            W4Cursor cur, pre;
+            w4_cursor_start(p, total_units, cur);
+            w4_cursor_advance(p, total_units, cur, w);
+            pre = cur;
+            auto request_raw = [&](const W4Cursor& c, int jj) {
+                const int r = jj % Cfg::R;
+                mbar_arrive_expect_tx(raw_full(r), W4_SLOT_BYTES);
+                tma_load_2d(raw_base + r * W4_SLOT_BYTES, &tmap_w, raw_full(r), 0, (c.kb * p.n_tiles + c.nt) * 4);
+                tma_load_2d(raw_base + r * W4_SLOT_BYTES + W4_RAW_BYTES, &tmap_sc, raw_full(r), c.nt * W4_TILE_N,
+                            c.kb / p.group_kb);
+            };
+            // prologue: this warp's first R / DQ blocks
+            for (int i = 0; i < Cfg::R / Cfg::DQ; ++i) {
+                if (pre.valid && lane == 0) request_raw(pre, w + i * Cfg::DQ);
+                w4_cursor_advance(p, total_units, pre, Cfg::DQ);
             }
-            if (!mbar_wait(st_empty(s), ph_s ^ 1u)) {
-                w4_report(p.status, 3, -j - 1);
-                break;
-            }
-            const uint32_t raw = raw_base + r * W4_RAW_BYTES;
-            const uint32_t wt = smem_base + s * Cfg::S_STAGE;
+            for (int j = w; cur.valid; j += Cfg::DQ) {
+                const int r = j % Cfg::R;
+                const int s = w;  // DQ == S: this warp owns stage w
+                const uint32_t ph_r = (j / Cfg::R) & 1;
+                const uint32_t ph_s = (j / Cfg::S) & 1;
+                if (!mbar_wait(st_empty(s), ph_s ^ 1u)) {
+                    w4_report(p.status, 3, -j - 1);
+                    break;
+                }
+                const uint32_t wt = smem_base + s * Cfg::S_STAGE;
+                if (lane == 0) {
+                    mbar_arrive_expect_tx(x_full(s), Cfg::X_BYTES);
+                    tma_load_2d(wt + W4_WT_BYTES, &tmap_x, x_full(s), cur.kb * W4_BK, cur.tt * BT);
+                }
+                if (!mbar_wait(raw_full(r), ph_r)) {
+                    w4_report(p.status, 3, j);
+                    break;
+                }
+                const uint32_t raw = raw_base + r * W4_SLOT_BYTES;
+                // Lane reads bytes [16 i, 16 i + 16) of the block for i = 32 q + lane, q = 0..7:
+                // row i / 2, 16-byte half i % 2 (conflict-free loads; the swizzled stores are too).
+                // All loads are issued before the first store so their latencies overlap.
+                uint4 v[8];
+                uint32_t sc_bits[8];
 #pragma unroll
-            for (int q = 0; q < 8; ++q) {
-                // lane reads bytes [16 i, 16 i + 16) of the block, i = 32 q + lane: row i / 2,
-                // 16-byte half i % 2 (conflict-free loads; the swizzled stores are too)
-                const int i = q * 32 + lane;
-                const uint32_t row = i >> 1;
-                const uint32_t c_base = (i & 1) * 4;
-                uint4 v;
-                asm volatile("ld.shared.v4.u32 {%0, %1, %2, %3}, [%4];"
-                             : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
-                             : "r"(raw + i * 16)
-                             : "memory");
-                const __half2 scale2 = __half2half2(sc_cur[q]);
-                dq_word_store(wt + sw128_offset(row, c_base + 0), v.x, scale2);
-                dq_word_store(wt + sw128_offset(row, c_base + 1), v.y, scale2);
-                dq_word_store(wt + sw128_offset(row, c_base + 2), v.z, scale2);
-                dq_word_store(wt + sw128_offset(row, c_base + 3), v.w, scale2);
-            }
-            // Every lane's stores consumed its loaded registers, so all loads of the packed
-            // block have completed; only now may the producer refill the slot.
-            fence_proxy_async_smem();
-            __syncwarp();
-            if (lane == 0) {
-                mbar_arrive(raw_empty(r));
-                mbar_arrive(wt_full(s));
-            }
-            cur = nxt;
+                for (int q = 0; q < 8; ++q) {
+                    const int i = q * 32 + lane;
+                    asm volatile("ld.shared.v4.u32 {%0, %1, %2, %3}, [%4];"
+                                 : "=r"(v[q].x), "=r"(v[q].y), "=r"(v[q].z), "=r"(v[q].w)
+                                 : "r"(raw + i * 16));
+                    asm volatile("ld.shared.u16 %0, [%1];" : "=r"(sc_bits[q]) : "r"(raw + W4_RAW_BYTES + (i >> 1) * 2));
+                }
 #pragma unroll
-            for (int q = 0; q < 8; ++q) sc_cur[q] = sc_next[q];
+                for (int q = 0; q < 8; ++q) {
+                    const int i = q * 32 + lane;
+                    const uint32_t row = i >> 1;
+                    const uint32_t c_base = (i & 1) * 4;
+                    const __half2 scale2 = __half2half2(__ushort_as_half(static_cast<unsigned short>(sc_bits[q])));
+                    dq_word_store(wt + sw128_offset(row, c_base + 0), v[q].x, scale2);
+                    dq_word_store(wt + sw128_offset(row, c_base + 1), v[q].y, scale2);
+                    dq_word_store(wt + sw128_offset(row, c_base + 2), v[q].z, scale2);
+                    dq_word_store(wt + sw128_offset(row, c_base + 3), v[q].w, scale2);
+                }
+                // Every lane's stores consumed its loaded registers, so all loads of the slot have
+                // completed before it is refilled below.
+                fence_proxy_async_smem();
+                __syncwarp();
+                if (lane == 0) {
+                    if constexpr (WM) {
+                        // Decode mode: this warp issues the MMAs of its own block into its own
+                        // accumulator (the epilogue adds the DQ accumulators), so no single thread
+                        // has to walk every block of the CTA.
+                        constexpr uint32_t idesc = make_idesc_f16_f32(W4_TILE_N, BT, false, false);
+                        const int u_idx = (cur.unit - static_cast<int>(blockIdx.x)) / static_cast<int>(gridDim.x);
+                        const int set = u_idx & 1;
+                        const bool first = (cur.kb - cur.kb0) < Cfg::DQ;
+                        const bool last = (cur.kb + Cfg::DQ) >= cur.kb1;
+                        bool good = mbar_wait(x_full(s), ph_s);
+                        if (good && first) good = mbar_wait(acc_empty(set), ((u_idx >> 1) & 1) ^ 1u);
+                        if (!good) w4_report(p.status, 5, j);
+                        tc_fence_after_sync();
+                        const uint32_t d_tmem = tmem_base + (set * Cfg::DQ + w) * BT;
+#pragma unroll
+                        for (int kk = 0; kk < W4_BK / 16; ++kk) {
+                            const uint64_t a_desc = make_smem_desc_sw128(wt + kk * 32, 16, 1024);
+                            const uint64_t b_desc = make_smem_desc_sw128(wt + W4_WT_BYTES + kk * 32, 16, 1024);
+                            umma_f16(d_tmem, a_desc, b_desc, idesc, (first && kk == 0) ? 0u : 1u);
+                        }
+                        umma_commit(st_empty(s));
+                        if (last) umma_commit(acc_full(set));
+                    } else {
+                        mbar_arrive(wt_full(s));
+                    }
+                    if (pre.valid) request_raw(pre, j + Cfg::R);
+                }
+                w4_cursor_advance(p, total_units, cur, Cfg::DQ);
+                w4_cursor_advance(p, total_units, pre, Cfg::DQ);
+            }
         }
     } else if (warp >= 12) {
         // ------------------------------------------------ epilogue warps
@@ -362,7 +354,7 @@ w4a16_gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const W4Params p) 
         for (int unit = blockIdx.x; unit < total_units; unit += gridDim.x) {
             int nt, tt, sl, kb0, kb1;
             w4_decode(p, unit, nt, tt, sl, kb0, kb1);
-            if (!mbar_wait(acc_full(acc), acc_ph)) {
+            if (!mbar_wait_relaxed(acc_full(acc), acc_ph, 256)) {
                 w4_report(p.status, 4, unit);
                 break;
             }
@@ -370,7 +362,7 @@ w4a16_gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const W4Params p) 
             const int n = nt * W4_TILE_N + row;
             const int t0 = tt * BT;
             const int tile_id = nt * p.t_tiles + tt;
-            const uint32_t t_addr = tmem_base + acc * BT + (static_cast<uint32_t>(quad * 32) << 16);
+            const uint32_t t_addr = tmem_base + acc * Cfg::ACCS * BT + (static_cast<uint32_t>(quad * 32) << 16);
             float* part = (p.split > 1)
                               ? p.partials + (static_cast<size_t>(tile_id) * p.split + sl) * (BT * 128)
                               : nullptr;
@@ -381,6 +373,18 @@ w4a16_gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const W4Params p) 
                 if constexpr (CH == 32) tmem_ld_32x32b_x32(t_addr + c * CH, v);
                 else tmem_ld_32x32b_x16(t_addr + c * CH, v);
                 tmem_wait_ld();
+                if constexpr (WM) {
+                    // add the other workers' accumulators in worker order
+#pragma unroll 1
+                    for (int a = 1; a < Cfg::ACCS; ++a) {
+                        uint32_t u[CH];
+                        if constexpr (CH == 32) tmem_ld_32x32b_x32(t_addr + a * BT + c * CH, u);
+                        else tmem_ld_32x32b_x16(t_addr + a * BT + c * CH, u);
+                        tmem_wait_ld();
+#pragma unroll
+                        for (int j = 0; j < CH; ++j) v[j] = __float_as_uint(__uint_as_float(v[j]) + __uint_as_float(u[j]));
+                    }
+                }
                 if (part != nullptr) {
 #pragma unroll
                     for (int j = 0; j < CH; ++j) part[(c * CH + j) * 128 + row] = __uint_as_float(v[j]);
@@ -456,7 +460,7 @@ int4_prepack_kernel(const uint8_t* __restrict__ codes, uint32_t* __restrict__ q,
         }
         words[j] = w;
     }
-    uint4* dst = reinterpret_cast<uint4*>(q + (static_cast<size_t>(nt) * (K / 64) + kb) * 1024 + r * 8);
+    uint4* dst = reinterpret_cast<uint4*>(q + (static_cast<size_t>(kb) * gridDim.y + nt) * 1024 + r * 8);
     dst[0] = make_uint4(words[0], words[1], words[2], words[3]);
     dst[1] = make_uint4(words[4], words[5], words[6], words[7]);
 }
@@ -469,7 +473,7 @@ int4_unpack_kernel(const uint32_t* __restrict__ q, const __half* __restrict__ sc
     const int kb = blockIdx.x, nt = blockIdx.y, r = threadIdx.x;
     const int n = nt * 128 + r;
     if (n >= N) return;
-    const uint4* src = reinterpret_cast<const uint4*>(q + (static_cast<size_t>(nt) * (K / 64) + kb) * 1024 + r * 8);
+    const uint4* src = reinterpret_cast<const uint4*>(q + (static_cast<size_t>(kb) * gridDim.y + nt) * 1024 + r * 8);
     const uint4 a = src[0], b = src[1];
     const uint32_t words[8] = {a.x, a.y, a.z, a.w, b.x, b.y, b.z, b.w};
 #pragma unroll
@@ -524,20 +528,21 @@ static int w4_select_split(int M, int N, int K, int sms) {
 
 static size_t w4_counter_bytes(int tiles) { return (static_cast<size_t>(tiles) * 4 + 255) / 256 * 256; }
 
-template <int BT>
-static int launch_w4(const CUtensorMap& tx, const W4Params& p, int sms, cudaStream_t stream) {
-    using Cfg = W4Cfg<BT>;
+template <int BT, bool WM>
+static int launch_w4(const CUtensorMap& tx, const CUtensorMap& tw, const CUtensorMap& tsc, const W4Params& p,
+                     int sms, cudaStream_t stream) {
+    using Cfg = W4Cfg<BT, WM>;
     static bool attr_set[64] = {};
     int dev = 0;
     WB_CHECK_CUDA(cudaGetDevice(&dev));
     if (dev >= 0 && dev < 64 && !attr_set[dev]) {
-        WB_CHECK_CUDA(cudaFuncSetAttribute(w4a16_gemm_kernel<BT>,
+        WB_CHECK_CUDA(cudaFuncSetAttribute(w4a16_gemm_kernel<BT, WM>,
                                            cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM_BYTES));
         attr_set[dev] = true;
     }
     const int units = p.n_tiles * p.t_tiles * p.split;
     const int grid = units < sms ? units : sms;
-    w4a16_gemm_kernel<BT><<<grid, W4_THREADS, Cfg::SMEM_BYTES, stream>>>(tx, p);
+    w4a16_gemm_kernel<BT, WM><<<grid, W4_THREADS, Cfg::SMEM_BYTES, stream>>>(tx, tw, tsc, p);
     WB_CHECK_CUDA(cudaGetLastError());
     return WMMA_OPS_OK;
 }
@@ -659,11 +664,22 @@ extern "C" int wmma_ops_w4a16_gemm(const void* A, const void* qweight, const voi
                         static_cast<uint64_t>(M), static_cast<uint64_t>(K) * 2, W4_BK, bt,
                         CU_TENSOR_MAP_SWIZZLE_128B);
     if (rc != WMMA_OPS_OK) return rc;
+    // qweight seen as int32 [4 * blocks][256]: one 4 KB block = a box of 4 rows x 1 KB
+    CUtensorMap tw, tsc;
+    rc = encode_tmap_2d(&tw, CU_TENSOR_MAP_DATA_TYPE_INT32, qweight, 256,
+                        static_cast<uint64_t>(p.n_tiles) * p.kb_total * 4, 1024, 256, 4, CU_TENSOR_MAP_SWIZZLE_NONE);
+    if (rc != WMMA_OPS_OK) return rc;
+    rc = encode_tmap_2d(&tsc, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, scales, static_cast<uint64_t>(N),
+                        static_cast<uint64_t>(K / group_size), static_cast<uint64_t>(N) * 2, W4_TILE_N, 1,
+                        CU_TENSOR_MAP_SWIZZLE_NONE);
+    if (rc != WMMA_OPS_OK) return rc;
+    // decode mode needs every K-slice to give each of the eight workers at least one block
+    const bool wm = bt <= 32 && (p.kb_total / p.split) >= 8;
     switch (bt) {
-        case 16: return launch_w4<16>(tx, p, sms, stream);
-        case 32: return launch_w4<32>(tx, p, sms, stream);
-        case 64: return launch_w4<64>(tx, p, sms, stream);
-        case 128: return launch_w4<128>(tx, p, sms, stream);
-        default: return launch_w4<256>(tx, p, sms, stream);
+        case 16: return wm ? launch_w4<16, true>(tx, tw, tsc, p, sms, stream) : launch_w4<16, false>(tx, tw, tsc, p, sms, stream);
+        case 32: return wm ? launch_w4<32, true>(tx, tw, tsc, p, sms, stream) : launch_w4<32, false>(tx, tw, tsc, p, sms, stream);
+        case 64: return launch_w4<64, false>(tx, tw, tsc, p, sms, stream);
+        case 128: return launch_w4<128, false>(tx, tw, tsc, p, sms, stream);
+        default: return launch_w4<256, false>(tx, tw, tsc, p, sms, stream);
     }
 }

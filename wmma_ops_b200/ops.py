@@ -159,10 +159,19 @@ def _matmul_impl(A, B, tile_cfg: int, split_k: int, where: str = "CUDA", same_de
 _DEFAULT_TILE = _lib.TILE_128x256
 
 
+def _main_tile(A, B) -> int:
+    """The tile of the main kernel: the 256x256 CTA pair when the product has at least one full
+    pair tile, else the 1-CTA 128x256 tile."""
+    try:
+        return _lib.TILE_256x256_PAIR if A.size(0) >= 256 and B.size(1) >= 256 else _DEFAULT_TILE
+    except Exception:
+        return _DEFAULT_TILE
+
+
 def matmul(A: torch.Tensor, B: torch.Tensor) -> torch.Tensor:
     """C = A @ B, fp16 inputs, fp32 output (wmma_matmul, wmma_gemm.hip:1432-1470).
     Fixed large tile, as the reference's matmul uses one fixed tile."""
-    return _matmul_impl(A, B, _DEFAULT_TILE, 1)
+    return _matmul_impl(A, B, _main_tile(A, B), 1)
 
 
 def matmul_adaptive(A: torch.Tensor, B: torch.Tensor) -> torch.Tensor:

@@ -34,12 +34,12 @@ def int4_prepack(codes: torch.Tensor, scales: torch.Tensor, group_size: int = 12
                  zero_point: int = ZERO_POINT) -> Tuple[torch.Tensor, torch.Tensor]:
     """Packs uint8 codes [K,N] (0..15) into the kernel's layout.
 
-    Returns (qweight int32 [ceil(N/128), K/64, 128, 8], scales fp16 [K/group_size, N] contiguous)."""
+    Returns (qweight int32 [K/64, ceil(N/128), 128, 8], scales fp16 [K/group_size, N] contiguous)."""
     _require(zero_point == ZERO_POINT, "only zero_point=8 is supported")
     K, N = _check_codes(codes, scales, group_size)
     codes = codes.contiguous()
     dev = codes.device
-    q = torch.empty(((N + 127) // 128, K // 64, 128, 8), dtype=torch.int32, device=dev)
+    q = torch.empty((K // 64, (N + 127) // 128, 128, 8), dtype=torch.int32, device=dev)
     with torch.cuda.device(dev):
         _lib.check(_lib.load().wmma_ops_int4_prepack(codes.data_ptr(), q.data_ptr(), K, N, _stream(dev)))
     return q, scales.contiguous()
@@ -48,9 +48,9 @@ def int4_prepack(codes: torch.Tensor, scales: torch.Tensor, group_size: int = 12
 def _qshape(qweight: torch.Tensor, N: int) -> Tuple[int, int]:
     _require(qweight.is_cuda and qweight.dtype == torch.int32 and qweight.dim() == 4
              and qweight.size(2) == 128 and qweight.size(3) == 8 and qweight.is_contiguous(),
-             "qweight must be a contiguous CUDA int32 tensor [ceil(N/128), K/64, 128, 8] from int4_prepack")
-    _require(qweight.size(0) == (N + 127) // 128, "qweight does not match N")
-    return qweight.size(1) * 64, N
+             "qweight must be a contiguous CUDA int32 tensor [K/64, ceil(N/128), 128, 8] from int4_prepack")
+    _require(qweight.size(1) == (N + 127) // 128, "qweight does not match N")
+    return qweight.size(0) * 64, N
 
 
 def int4_unpack(qweight: torch.Tensor, N: int) -> torch.Tensor:
