@@ -196,17 +196,37 @@ def run_reference_arm(args):
 
 
 # ----------------------------------------------------------------------------- other north-star figures
-def _time_calls(fns, iters, world, dev):
-    """ms per call, cycling through `fns` (distinct buffers defeat the L2 for HBM-bound rows)."""
+def _time_calls(fns, iters, world, dev, graph=False):
+    """ms per call, cycling through `fns` (distinct buffers defeat the L2 for HBM-bound rows).
+    graph=True replays the calls from a CUDA graph so that microsecond kernels are not timed
+    through the host's per-call overhead."""
     for f in fns:
         f()
+    torch.cuda.synchronize()
+    run = None
+    if graph:
+        side = torch.cuda.Stream()
+        side.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(side):
+            for f in fns:
+                f()
+        torch.cuda.current_stream().wait_stream(side)
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g):
+            for f in fns:
+                f()
+        run = g.replay
+        run()
     barrier_sync(world)
     e0 = torch.cuda.Event(enable_timing=True)
     e1 = torch.cuda.Event(enable_timing=True)
     e0.record()
     for _ in range(iters):
-        for f in fns:
-            f()
+        if run is not None:
+            run()
+        else:
+            for f in fns:
+                f()
     e1.record()
     barrier_sync(world)
     return max_over_ranks(e0.elapsed_time(e1), world, dev) / (iters * len(fns))
@@ -229,11 +249,11 @@ def measure_w4a16(w, dev, peaks, world):
     for M in (1, 16, 128, 4096):
         A = torch.randn(M, K, generator=gen, device=dev).half()
         fns = [(lambda q=q, sc=sc: w.matmul_w4a16(A, q, sc, g)) for q, sc in weights]
-        ms = _time_calls(fns, 3 if M > 128 else 10, world, dev)
+        ms = _time_calls(fns, 3 if M > 128 else 10, world, dev, graph=M <= 128)
         by = int4.w4a16_bytes(M, N, K, g)
         gbs, tf = by / ms / 1e6, 2.0 * M * N * K / ms / 1e9
         rows[f"M{M}"] = {"us": ms * 1e3, "gbs": gbs, "tflops": tf, "hbm_frac": gbs / peaks["hbm_gbs"],
-                         "tensor_frac": tf / peaks["tflops"]}
+                         "tensor_frac": tf / peaks["tflops"], "timed": "cuda graph replay" if M <= 128 else "eager launches"}
     return rows
 
 

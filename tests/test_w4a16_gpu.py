@@ -83,6 +83,21 @@ def test_config3_decode_shapes(cuda, M):
     assert _w4_case(cuda, M, 11008, 4096, 128, 0) < TOL
 
 
+@pytest.mark.parametrize("case", [(3, 1000, 2048), (16, 4096, 4096), (1, 256, 8192), (20, 2048, 1024), (2, 8, 1024)])
+def test_decode_with_few_column_tiles_uses_the_balanced_plan(cuda, case):
+    # few column tiles: k-blocks are dealt to all SMs in equal runs and the partial sums of a
+    # tile are combined by the last CTA to arrive, in slice order (deterministic)
+    M, N, K = case
+    codes, scales = int4.seeded_w4(K, N, 128, seed=11)
+    A, _ = og.seeded_ab(M, 8, K, seed=12)
+    q, sc = w.int4_prepack(codes.to(cuda), scales.to(cuda), 128)
+    ref = int4.w4a16_ref(A, codes, scales, 128)
+    outs = [w.matmul_w4a16(A.to(cuda), q, sc, 128) for _ in range(3)]
+    _sync_ok()
+    assert og.rel_frobenius(outs[0], ref) < TOL
+    assert torch.equal(outs[0], outs[1]) and torch.equal(outs[1], outs[2])
+
+
 def test_config3_prefill_shape_repeated(cuda):
     # M = 4096: every CTA walks several tiles; repeated to catch timing-dependent faults
     M, N, K, group = 4096, 11008, 4096, 128

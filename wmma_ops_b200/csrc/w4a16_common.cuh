@@ -1,0 +1,137 @@
+// Definitions of the W4A16 kernel (w4a16_sm100.cu): launch parameters, the walk over work units
+// and the exact dequant step.
+#pragma once
+#include <cuda.h>
+#include <cuda_fp16.h>
+#include <cstdint>
+
+#include "ptx.cuh"
+
+namespace wb {
+
+constexpr int W4_TILE_N = 128;     // weight columns per CTA tile (MMA M)
+constexpr int W4_BK = 64;          // k per pipeline step
+constexpr int W4_RAW_BYTES = 4096; // one packed block
+constexpr int W4_SLOT_BYTES = W4_RAW_BYTES + W4_TILE_N * 2;  // + the block's 128 fp16 scales
+constexpr int W4_WT_BYTES = W4_TILE_N * W4_BK * 2;
+constexpr int W4_THREADS = 512;
+constexpr int W4_DQ_WARPS = 8;     // each dequant warp expands a whole 4 KB block; 8 blocks in flight
+
+struct W4Params {
+    const uint32_t* qweight;
+    const __half* scales;
+    float* C;
+    float* partials;   // [tiles][split][BT][128]
+    int* counters;     // [tiles]
+    int M, N, K;
+    int n_tiles, t_tiles, split;
+    int balanced;      // 1: k-blocks are dealt to the CTAs in equal runs of 8-block chunks (decode)
+    int max_slices;    // slices a tile can have (= split in the classic plan): stride of partials
+    int kb_total;
+    int group_kb;      // k-blocks per scale group (group_size / 64)
+    int* status;
+};
+
+__device__ __forceinline__ void w4_report(int* status, int role, int detail) {
+    if (status != nullptr && atomicCAS(status, 0, 2) == 0) {
+        status[1] = role;
+        status[2] = static_cast<int>(blockIdx.x);
+        status[3] = detail;
+    }
+}
+
+// One work unit of a CTA: the k-blocks [kb0, kb1) of the tile (nt, tt); it is slice `sl` of `nsl`
+// slices of that tile.
+struct W4Unit {
+    int nt, tt, sl, nsl, kb0, kb1;
+};
+
+constexpr int W4_CHUNK = 8;  // k-blocks per chunk in the balanced plan
+
+// CTA that owns chunk x when total chunks TC are dealt to G CTAs in runs [c*TC/G, (c+1)*TC/G).
+__device__ __forceinline__ int w4_chunk_owner(long long x, long long TC, long long G) {
+    long long c = x * G / TC;
+    while ((c + 1) * TC / G <= x) ++c;
+    while (c * TC / G > x) --c;
+    return static_cast<int>(c);
+}
+
+// The ui-th work unit of this CTA (ui = 0, 1, ...). Returns false past the last one.
+// Classic plan: units (tile, K-slice) are dealt round-robin, unit = blockIdx.x + ui * gridDim.x.
+// Balanced plan (decode, one token tile): all k-blocks of all column tiles, in tile-major order and
+// cut into chunks of 8, are dealt to the CTAs in equal contiguous runs, so every SM streams the
+// same number of bytes; a run covers parts of one to three tiles and each part is a unit.
+__device__ __forceinline__ bool w4_unit(const W4Params& p, int ui, W4Unit& u) {
+    if (!p.balanced) {
+        const int unit = static_cast<int>(blockIdx.x) + ui * static_cast<int>(gridDim.x);
+        if (unit >= p.n_tiles * p.t_tiles * p.split) return false;
+        u.sl = unit % p.split;
+        u.nsl = p.split;
+        const int t = unit / p.split;
+        u.tt = t % p.t_tiles;
+        u.nt = t / p.t_tiles;
+        u.kb0 = static_cast<int>(static_cast<long long>(u.sl) * p.kb_total / p.split);
+        u.kb1 = static_cast<int>(static_cast<long long>(u.sl + 1) * p.kb_total / p.split);
+        return true;
+    }
+    const long long cpt = p.kb_total / W4_CHUNK;  // chunks per tile
+    const long long TC = cpt * p.n_tiles;
+    const long long G = gridDim.x;
+    const long long c0 = static_cast<long long>(blockIdx.x) * TC / G;
+    const long long c1 = static_cast<long long>(blockIdx.x + 1) * TC / G;
+    const long long tile = c0 / cpt + ui;
+    const long long start = c0 > tile * cpt ? c0 : tile * cpt;
+    const long long end = c1 < (tile + 1) * cpt ? c1 : (tile + 1) * cpt;
+    if (start >= end) return false;
+    u.nt = static_cast<int>(tile);
+    u.tt = 0;
+    u.kb0 = static_cast<int>(start - tile * cpt) * W4_CHUNK;
+    u.kb1 = static_cast<int>(end - tile * cpt) * W4_CHUNK;
+    const int c_first = w4_chunk_owner(tile * cpt, TC, G);
+    const int c_last = w4_chunk_owner((tile + 1) * cpt - 1, TC, G);
+    u.sl = static_cast<int>(blockIdx.x) - c_first;
+    u.nsl = c_last - c_first + 1;
+    return true;
+}
+
+// Position of a worker warp in the CTA's sequence of k-block iterations.
+struct W4Cursor {
+    int ui, nt, tt, kb, kb0, kb1;
+    bool valid;
+};
+
+__device__ __forceinline__ void w4_cursor_start(const W4Params& p, W4Cursor& c) {
+    W4Unit u;
+    c.ui = 0;
+    c.valid = w4_unit(p, 0, u);
+    c.nt = u.nt; c.tt = u.tt; c.kb = c.kb0 = u.kb0; c.kb1 = u.kb1;
+}
+
+// Moves the cursor `steps` iterations forward, crossing into later work units as needed.
+__device__ __forceinline__ void w4_cursor_advance(const W4Params& p, W4Cursor& c, int steps) {
+    if (!c.valid) return;
+    c.kb += steps;
+    while (c.kb >= c.kb1) {
+        const int over = c.kb - c.kb1;
+        W4Unit u;
+        if (!w4_unit(p, ++c.ui, u)) {
+            c.valid = false;
+            return;
+        }
+        c.nt = u.nt; c.tt = u.tt; c.kb0 = u.kb0; c.kb1 = u.kb1;
+        c.kb = c.kb0 + over;
+    }
+}
+
+// (code - 8) * scale for the two codes that sit 16 bits apart in t (already masked):
+// 0x6400 | code is the fp16 number 1024 + code, so subtracting 1032 gives code - 8 exactly;
+// the product is one fp16 multiply (round to nearest even).
+__device__ __forceinline__ uint32_t dq_pair(uint32_t t, __half2 scale2) {
+    const uint32_t h = t | 0x64006400u;
+    const __half2 v = __hsub2(*reinterpret_cast<const __half2*>(&h), __half2half2(__ushort_as_half(0x6408)));
+    const __half2 r = __hmul2(v, scale2);
+    return *reinterpret_cast<const uint32_t*>(&r);
+}
+
+
+}  // namespace wb

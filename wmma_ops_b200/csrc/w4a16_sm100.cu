@@ -21,18 +21,13 @@
 // Warps: 2 MMA issuer + TMEM owner; 4..11 workers (each requests, expands and hands over whole
 // 4 KB blocks); 12..15 epilogue; 0, 1, 3 idle.  Split-K partials are combined by the last CTA to finish a
 // tile (arrival counter, no waiting), summed in ascending slice order.
+#include <cstdlib>
+
 #include "host_common.cuh"
 #include "ptx.cuh"
+#include "w4a16_common.cuh"
 
 namespace wb {
-
-constexpr int W4_TILE_N = 128;     // weight columns per CTA tile (MMA M)
-constexpr int W4_BK = 64;          // k per pipeline step
-constexpr int W4_RAW_BYTES = 4096; // one packed block
-constexpr int W4_SLOT_BYTES = W4_RAW_BYTES + W4_TILE_N * 2;  // + the block's 128 fp16 scales
-constexpr int W4_WT_BYTES = W4_TILE_N * W4_BK * 2;
-constexpr int W4_THREADS = 512;
-constexpr int W4_DQ_WARPS = 8;     // each dequant warp expands a whole 4 KB block; 8 blocks in flight
 
 template <int BT, bool WM>
 struct W4Cfg {
@@ -54,80 +49,6 @@ struct W4Cfg {
     static constexpr int SMEM_BYTES = S * S_STAGE + R * W4_SLOT_BYTES + 1024 + 512;
 };
 
-struct W4Params {
-    const uint32_t* qweight;
-    const __half* scales;
-    float* C;
-    float* partials;   // [tiles][split][BT][128]
-    int* counters;     // [tiles]
-    int M, N, K;
-    int n_tiles, t_tiles, split;
-    int kb_total;
-    int group_kb;      // k-blocks per scale group (group_size / 64)
-    int* status;
-};
-
-__device__ __forceinline__ void w4_report(int* status, int role, int detail) {
-    if (status != nullptr && atomicCAS(status, 0, 2) == 0) {
-        status[1] = role;
-        status[2] = static_cast<int>(blockIdx.x);
-        status[3] = detail;
-    }
-}
-
-__device__ __forceinline__ void w4_decode(const W4Params& p, int unit, int& nt, int& tt, int& sl,
-                                          int& kb0, int& kb1) {
-    sl = unit % p.split;
-    const int t = unit / p.split;
-    tt = t % p.t_tiles;
-    nt = t / p.t_tiles;
-    kb0 = static_cast<int>(static_cast<long long>(sl) * p.kb_total / p.split);
-    kb1 = static_cast<int>(static_cast<long long>(sl + 1) * p.kb_total / p.split);
-}
-
-// Position of a worker warp in the CTA's sequence of k-block iterations.
-struct W4Cursor {
-    int unit, nt, tt, kb, kb0, kb1;
-    bool valid;
-};
-
-__device__ __forceinline__ void w4_cursor_start(const W4Params& p, int total_units, W4Cursor& c) {
-    c.unit = blockIdx.x;
-    c.valid = c.unit < total_units;
-    c.nt = c.tt = c.kb = c.kb0 = c.kb1 = 0;
-    if (c.valid) {
-        int sl;
-        w4_decode(p, c.unit, c.nt, c.tt, sl, c.kb0, c.kb1);
-        c.kb = c.kb0;
-    }
-}
-
-// Moves the cursor `steps` iterations forward, crossing into later work units as needed.
-__device__ __forceinline__ void w4_cursor_advance(const W4Params& p, int total_units, W4Cursor& c, int steps) {
-    if (!c.valid) return;
-    c.kb += steps;
-    while (c.kb >= c.kb1) {
-        const int over = c.kb - c.kb1;
-        c.unit += gridDim.x;
-        if (c.unit >= total_units) {
-            c.valid = false;
-            return;
-        }
-        int sl;
-        w4_decode(p, c.unit, c.nt, c.tt, sl, c.kb0, c.kb1);
-        c.kb = c.kb0 + over;
-    }
-}
-
-// (code - 8) * scale for the two codes that sit 16 bits apart in t (already masked):
-// 0x6400 | code is the fp16 number 1024 + code, so subtracting 1032 gives code - 8 exactly;
-// the product is one fp16 multiply (round to nearest even).
-__device__ __forceinline__ uint32_t dq_pair(uint32_t t, __half2 scale2) {
-    const uint32_t h = t | 0x64006400u;
-    const __half2 v = __hsub2(*reinterpret_cast<const __half2*>(&h), __half2half2(__ushort_as_half(0x6408)));
-    const __half2 r = __hmul2(v, scale2);
-    return *reinterpret_cast<const uint32_t*>(&r);
-}
 
 __device__ __forceinline__ void dq_word_store(uint32_t dst, uint32_t w, __half2 scale2) {
     const uint32_t a = dq_pair(w & 0x000F000Fu, scale2);
@@ -188,7 +109,6 @@ w4a16_gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_const
     uint32_t tmem_base;
     asm volatile("ld.shared.u32 %0, [%1];" : "=r"(tmem_base) : "r"(tmem_slot) : "memory");
 
-    const int total_units = p.n_tiles * p.t_tiles * p.split;
 
     if (warp == 2) {
         // ------------------------------------------------ MMA issuer
@@ -199,9 +119,9 @@ w4a16_gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_const
             int acc = 0;
             uint32_t acc_ph = 0;
             bool ok = true;
-            for (int unit = blockIdx.x; ok && unit < total_units; unit += gridDim.x) {
-                int nt, tt, sl, kb0, kb1;
-                w4_decode(p, unit, nt, tt, sl, kb0, kb1);
+            W4Unit U;
+            for (int ui = 0; ok && w4_unit(p, ui, U); ++ui) {
+                const int kb0 = U.kb0, kb1 = U.kb1;
                 if (!mbar_wait(acc_empty(acc), acc_ph ^ 1u)) {
                     w4_report(p.status, 2, -1);
                     break;
@@ -250,8 +170,8 @@ w4a16_gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_const
         const int w = warp - 4;
         if (w < Cfg::DQ) {
             W4Cursor cur, pre;
-            w4_cursor_start(p, total_units, cur);
-            w4_cursor_advance(p, total_units, cur, w);
+            w4_cursor_start(p, cur);
+            w4_cursor_advance(p, cur, w);
             pre = cur;
             auto request_raw = [&](const W4Cursor& c, int jj) {
                 const int r = jj % Cfg::R;
@@ -263,7 +183,7 @@ w4a16_gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_const
             // prologue: this warp's first R / DQ blocks
             for (int i = 0; i < Cfg::R / Cfg::DQ; ++i) {
                 if (pre.valid && lane == 0) request_raw(pre, w + i * Cfg::DQ);
-                w4_cursor_advance(p, total_units, pre, Cfg::DQ);
+                w4_cursor_advance(p, pre, Cfg::DQ);
             }
             for (int j = w; cur.valid; j += Cfg::DQ) {
                 const int r = j % Cfg::R;
@@ -318,7 +238,7 @@ w4a16_gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_const
                         // accumulator (the epilogue adds the DQ accumulators), so no single thread
                         // has to walk every block of the CTA.
                         constexpr uint32_t idesc = make_idesc_f16_f32(W4_TILE_N, BT, false, false);
-                        const int u_idx = (cur.unit - static_cast<int>(blockIdx.x)) / static_cast<int>(gridDim.x);
+                        const int u_idx = cur.ui;
                         const int set = u_idx & 1;
                         const bool first = (cur.kb - cur.kb0) < Cfg::DQ;
                         const bool last = (cur.kb + Cfg::DQ) >= cur.kb1;
@@ -340,8 +260,8 @@ w4a16_gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_const
                     }
                     if (pre.valid) request_raw(pre, j + Cfg::R);
                 }
-                w4_cursor_advance(p, total_units, cur, Cfg::DQ);
-                w4_cursor_advance(p, total_units, pre, Cfg::DQ);
+                w4_cursor_advance(p, cur, Cfg::DQ);
+                w4_cursor_advance(p, pre, Cfg::DQ);
             }
         }
     } else if (warp >= 12) {
@@ -351,11 +271,11 @@ w4a16_gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_const
         const int et = threadIdx.x - 384;  // 0..127
         int acc = 0;
         uint32_t acc_ph = 0;
-        for (int unit = blockIdx.x; unit < total_units; unit += gridDim.x) {
-            int nt, tt, sl, kb0, kb1;
-            w4_decode(p, unit, nt, tt, sl, kb0, kb1);
+        W4Unit U;
+        for (int ui = 0; w4_unit(p, ui, U); ++ui) {
+            const int nt = U.nt, tt = U.tt, sl = U.sl, nsl = U.nsl;
             if (!mbar_wait_relaxed(acc_full(acc), acc_ph, 256)) {
-                w4_report(p.status, 4, unit);
+                w4_report(p.status, 4, ui);
                 break;
             }
             tc_fence_after_sync();
@@ -363,8 +283,8 @@ w4a16_gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_const
             const int t0 = tt * BT;
             const int tile_id = nt * p.t_tiles + tt;
             const uint32_t t_addr = tmem_base + acc * Cfg::ACCS * BT + (static_cast<uint32_t>(quad * 32) << 16);
-            float* part = (p.split > 1)
-                              ? p.partials + (static_cast<size_t>(tile_id) * p.split + sl) * (BT * 128)
+            float* part = (nsl > 1)
+                              ? p.partials + (static_cast<size_t>(tile_id) * p.max_slices + sl) * (BT * 128)
                               : nullptr;
             constexpr int CH = (BT >= 32) ? 32 : 16;
 #pragma unroll 1
@@ -401,13 +321,13 @@ w4a16_gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_const
             acc ^= 1;
             if (acc == 0) acc_ph ^= 1u;
 
-            if (p.split > 1) {
+            if (nsl > 1) {
                 // the last slice of this tile to finish sums all partials in slice order
                 __threadfence();
                 named_barrier_sync(1, 128);
                 if (et == 0) {
                     const int old = atomicAdd(p.counters + tile_id, 1);
-                    const uint32_t last = (old == p.split - 1) ? 1u : 0u;
+                    const uint32_t last = (old == nsl - 1) ? 1u : 0u;
                     if (last) p.counters[tile_id] = 0;  // ready for the next call
                     asm volatile("st.shared.u32 [%0], %1;" ::"r"(flag_slot), "r"(last) : "memory");
                 }
@@ -416,14 +336,26 @@ w4a16_gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_const
                 asm volatile("ld.shared.u32 %0, [%1];" : "=r"(last) : "r"(flag_slot) : "memory");
                 if (last) {
                     __threadfence();
-                    const float* base = p.partials + static_cast<size_t>(tile_id) * p.split * (BT * 128);
+                    const float* base = p.partials + static_cast<size_t>(tile_id) * p.max_slices * (BT * 128);
                     const int t_count = min(BT, p.M - t0);
                     if (n < p.N) {
-                        for (int t = 0; t < t_count; ++t) {
-                            float sum = 0.f;
-                            for (int s2 = 0; s2 < p.split; ++s2)
-                                sum += __ldcg(base + (static_cast<size_t>(s2) * BT + t) * 128 + row);
-                            p.C[static_cast<size_t>(t0 + t) * p.N + n] = sum;
+                        // eight tokens at a time so that the loads of a slice are all in flight
+                        // together; every element is still summed in ascending slice order
+                        for (int tb = 0; tb < t_count; tb += 8) {
+                            float sum[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+                            for (int s2 = 0; s2 < nsl; ++s2) {
+                                float v[8];
+#pragma unroll
+                                for (int u = 0; u < 8; ++u)
+                                    v[u] = (tb + u < t_count)
+                                               ? __ldcg(base + (static_cast<size_t>(s2) * BT + tb + u) * 128 + row)
+                                               : 0.f;
+#pragma unroll
+                                for (int u = 0; u < 8; ++u) sum[u] += v[u];
+                            }
+#pragma unroll
+                            for (int u = 0; u < 8; ++u)
+                                if (tb + u < t_count) p.C[static_cast<size_t>(t0 + tb + u) * p.N + n] = sum[u];
                         }
                     }
                 }
@@ -502,35 +434,65 @@ static int w4_pick_bt(int M) {
 }
 
 static int w4_select_split(int M, int N, int K, int sms) {
-    const int bt = w4_pick_bt(M);
-    const int tiles = ((N + 127) / 128) * ((M + bt - 1) / bt);
-    const int kb_total = K / 64;
-    // Measured on B200 (N=11008, K=4096): the partial-sum traffic and the serial reduce of the
-    // last CTA cost more than the idle SMs save once a tile holds more than a few tokens.
-    if (tiles >= sms || kb_total < 16 || M > 4) return 1;
-    int best = 1;
-    double best_cost = 0.0;
-    const int max_split = kb_total / 8 < 16 ? kb_total / 8 : 16;
-    for (int s = 1; s <= max_split; ++s) {
-        const int units = tiles * s;
-        const int waves = (units + sms - 1) / sms;
-        const int per = (kb_total + s - 1) / s;
-        // a unit costs its k-blocks plus a fixed fill/drain of about six k-blocks,
-        // and each extra slice adds partial traffic proportional to the token tile
-        const double cost = waves * (per + 6.0 + (s > 1 ? 0.02 * bt : 0.0));
-        if (s == 1 || cost < best_cost) {
-            best_cost = cost;
-            best = s;
-        }
-    }
-    return best;
+    // Measured on B200 (N = 11008, K = 4096, M = 1..128): cutting K into slices never paid for
+    // itself (each slice adds a partial-sum hand-over worth about 25 k-blocks); the balanced plan
+    // in w4_make_plan covers the case of too few column tiles. An explicit split_k still works.
+    (void)M; (void)N; (void)K; (void)sms;
+    return 1;
 }
 
 static size_t w4_counter_bytes(int tiles) { return (static_cast<size_t>(tiles) * 4 + 255) / 256 * 256; }
 
+// How a product is cut into work units.
+struct W4Plan {
+    int bt, n_tiles, t_tiles, kb_total;
+    int split;       // K-slices per tile in the classic plan
+    int balanced;    // 1: equal runs of 8-block chunks per CTA (see w4_unit)
+    int max_slices;  // slices a tile can have
+    int grid;
+    bool partials() const { return balanced || split > 1; }
+    size_t workspace_bytes() const {
+        if (!partials()) return 0;
+        const int tiles = n_tiles * t_tiles;
+        return w4_counter_bytes(tiles) + static_cast<size_t>(tiles) * max_slices * bt * 128 * sizeof(float);
+    }
+};
+
+static W4Plan w4_make_plan(int M, int N, int K, int split_k, int sms) {
+    W4Plan pl;
+    pl.bt = w4_pick_bt(M);
+    pl.n_tiles = (N + 127) / 128;
+    pl.t_tiles = (M + pl.bt - 1) / pl.bt;
+    pl.kb_total = K / 64;
+    pl.balanced = 0;
+    // Balanced plan only when the column tiles alone would leave most SMs idle: measured on B200
+    // (K = 4096) its partial-sum hand-over costs about as much as 25 k-blocks, so with 86 tiles on
+    // 148 SMs the plain plan (one whole tile per CTA) is as fast and needs no workspace.
+    if (split_k == 0 && pl.bt <= 32 && pl.t_tiles == 1 && pl.kb_total % W4_CHUNK == 0 && pl.kb_total >= 2 * W4_CHUNK &&
+        2 * pl.n_tiles <= sms) {
+        // deal chunks of 8 k-blocks to the SMs in equal runs
+        const int cpt = pl.kb_total / W4_CHUNK;
+        const long long total_chunks = static_cast<long long>(cpt) * pl.n_tiles;
+        pl.grid = total_chunks < sms ? static_cast<int>(total_chunks) : sms;
+        const int per = static_cast<int>(total_chunks / pl.grid);  // >= 1
+        pl.balanced = 1;
+        pl.split = 1;
+        pl.max_slices = (cpt + per - 1) / per + 1;
+        return pl;
+    }
+    int split = split_k == 0 ? w4_select_split(M, N, K, sms) : split_k;
+    if (split < 1) split = 1;
+    if (split > pl.kb_total) split = pl.kb_total;
+    pl.split = split;
+    pl.max_slices = split;
+    const long long units = static_cast<long long>(pl.n_tiles) * pl.t_tiles * split;
+    pl.grid = units < sms ? static_cast<int>(units) : sms;
+    return pl;
+}
+
 template <int BT, bool WM>
 static int launch_w4(const CUtensorMap& tx, const CUtensorMap& tw, const CUtensorMap& tsc, const W4Params& p,
-                     int sms, cudaStream_t stream) {
+                     int grid, cudaStream_t stream) {
     using Cfg = W4Cfg<BT, WM>;
     static bool attr_set[64] = {};
     int dev = 0;
@@ -540,8 +502,6 @@ static int launch_w4(const CUtensorMap& tx, const CUtensorMap& tw, const CUtenso
                                            cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM_BYTES));
         attr_set[dev] = true;
     }
-    const int units = p.n_tiles * p.t_tiles * p.split;
-    const int grid = units < sms ? units : sms;
     w4a16_gemm_kernel<BT, WM><<<grid, W4_THREADS, Cfg::SMEM_BYTES, stream>>>(tx, tw, tsc, p);
     WB_CHECK_CUDA(cudaGetLastError());
     return WMMA_OPS_OK;
@@ -602,11 +562,8 @@ extern "C" int wmma_ops_w4a16_select_split(int M, int N, int K, int num_sms) {
 }
 
 extern "C" size_t wmma_ops_w4a16_workspace_bytes(int M, int N, int K, int split_k) {
-    (void)K;
-    if (split_k <= 1 || M < 1 || N < 1) return 0;
-    const int bt = wb::w4_pick_bt(M);
-    const int tiles = ((N + 127) / 128) * ((M + bt - 1) / bt);
-    return wb::w4_counter_bytes(tiles) + static_cast<size_t>(tiles) * split_k * bt * 128 * sizeof(float);
+    if (M < 1 || N < 8 || K < 64 || K % 64 != 0) return 0;
+    return wb::w4_make_plan(M, N, K, split_k, wb::sm_count()).workspace_bytes();
 }
 
 extern "C" int wmma_ops_w4a16_gemm(const void* A, const void* qweight, const void* scales, void* C, int M,
@@ -629,7 +586,8 @@ extern "C" int wmma_ops_w4a16_gemm(const void* A, const void* qweight, const voi
                "scales must be 16-byte aligned");
 
     const int sms = sm_count();
-    const int bt = w4_pick_bt(M);
+    const W4Plan plan = w4_make_plan(M, N, K, split_k, sms);
+    const int bt = plan.bt;
     W4Params p;
     p.qweight = static_cast<const uint32_t*>(qweight);
     p.scales = static_cast<const __half*>(scales);
@@ -637,22 +595,22 @@ extern "C" int wmma_ops_w4a16_gemm(const void* A, const void* qweight, const voi
     p.M = M;
     p.N = N;
     p.K = K;
-    p.n_tiles = (N + 127) / 128;
-    p.t_tiles = (M + bt - 1) / bt;
-    p.kb_total = K / 64;
+    p.n_tiles = plan.n_tiles;
+    p.t_tiles = plan.t_tiles;
+    p.kb_total = plan.kb_total;
     p.group_kb = group_size / 64;
     p.status = status;
-    if (split_k == 0) split_k = w4_select_split(M, N, K, sms);
-    if (split_k < 1) split_k = 1;
-    if (split_k > p.kb_total) split_k = p.kb_total;
-    p.split = split_k;
+    p.split = plan.split;
+    p.balanced = plan.balanced;
+    p.max_slices = plan.max_slices;
     p.partials = nullptr;
     p.counters = nullptr;
-    if (split_k > 1) {
-        const size_t need = wmma_ops_w4a16_workspace_bytes(M, N, K, split_k);
+    if (plan.partials()) {
+        const size_t need = plan.workspace_bytes();
         WB_REQUIRE(workspace != nullptr && workspace_bytes >= need, WMMA_OPS_ERR_WORKSPACE,
-                   "w4a16: split_k=%d needs %zu bytes of zero-initialised workspace (got %zu)", split_k, need,
-                   workspace_bytes);
+                   "w4a16: this product is cut into partial sums and needs %zu bytes of zero-initialised workspace "
+                   "(got %zu); see wmma_ops_w4a16_workspace_bytes",
+                   need, workspace_bytes);
         WB_REQUIRE(reinterpret_cast<uintptr_t>(workspace) % 16 == 0, WMMA_OPS_ERR_INVALID,
                    "workspace must be 16-byte aligned");
         p.counters = static_cast<int*>(workspace);
@@ -673,13 +631,15 @@ extern "C" int wmma_ops_w4a16_gemm(const void* A, const void* qweight, const voi
                         static_cast<uint64_t>(K / group_size), static_cast<uint64_t>(N) * 2, W4_TILE_N, 1,
                         CU_TENSOR_MAP_SWIZZLE_NONE);
     if (rc != WMMA_OPS_OK) return rc;
-    // decode mode needs every K-slice to give each of the eight workers at least one block
-    const bool wm = bt <= 32 && (p.kb_total / p.split) >= 8;
+    // decode mode (workers issue their own MMAs) needs every unit to give each of the eight
+    // workers at least one block; the balanced plan's units are whole 8-block chunks
+    const bool wm = bt <= 32 && (plan.balanced || (p.kb_total / p.split) >= 8);
+    const int grid = plan.grid;
     switch (bt) {
-        case 16: return wm ? launch_w4<16, true>(tx, tw, tsc, p, sms, stream) : launch_w4<16, false>(tx, tw, tsc, p, sms, stream);
-        case 32: return wm ? launch_w4<32, true>(tx, tw, tsc, p, sms, stream) : launch_w4<32, false>(tx, tw, tsc, p, sms, stream);
-        case 64: return launch_w4<64, false>(tx, tw, tsc, p, sms, stream);
-        case 128: return launch_w4<128, false>(tx, tw, tsc, p, sms, stream);
-        default: return launch_w4<256, false>(tx, tw, tsc, p, sms, stream);
+        case 16: return wm ? launch_w4<16, true>(tx, tw, tsc, p, grid, stream) : launch_w4<16, false>(tx, tw, tsc, p, grid, stream);
+        case 32: return wm ? launch_w4<32, true>(tx, tw, tsc, p, grid, stream) : launch_w4<32, false>(tx, tw, tsc, p, grid, stream);
+        case 64: return launch_w4<64, false>(tx, tw, tsc, p, grid, stream);
+        case 128: return launch_w4<128, false>(tx, tw, tsc, p, grid, stream);
+        default: return launch_w4<256, false>(tx, tw, tsc, p, grid, stream);
     }
 }

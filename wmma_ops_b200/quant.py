@@ -99,11 +99,9 @@ def matmul_w4a16(A: torch.Tensor, qweight: torch.Tensor, scales: torch.Tensor, g
     if M == 0:
         return C
     with torch.cuda.device(dev):
-        if split_k == 0:
-            split_k = lib.wmma_ops_w4a16_select_split(M, N, K, _sm_count(dev))
         ws_ptr, ws_bytes = None, 0
-        if split_k > 1:
-            need = lib.wmma_ops_w4a16_workspace_bytes(M, N, K, split_k)
+        need = lib.wmma_ops_w4a16_workspace_bytes(M, N, K, split_k)   # split_k = 0: the library's own plan
+        if need > 0:
             ws = _workspace(dev, need, zero_init=True)
             ws_ptr, ws_bytes = ws.data_ptr(), ws.numel()
         rc = lib.wmma_ops_w4a16_gemm(A.data_ptr(), qweight.data_ptr(), scales.data_ptr(), C.data_ptr(), M, N, K,
