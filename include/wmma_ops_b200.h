@@ -127,6 +127,20 @@ int wmma_ops_w4a16_gemm(const void* A, const void* qweight, const void* scales, 
                         int N, int K, int group_size, int split_k, void* workspace,
                         size_t workspace_bytes, int* status, void* stream);
 
+/* wmma_ops_w4a16_gemm with a fused output stage (no counterpart in the reference):
+ *   WMMA_OPS_W4_OUT_F32           C fp32 [M,N] = acc                      (what wmma_ops_w4a16_gemm does)
+ *   WMMA_OPS_W4_OUT_F16           C fp16 [M,N] = half(alpha * acc)
+ *   WMMA_OPS_W4_OUT_F16_SILU_MUL  C fp16 [M,N/2] = half(alpha * silu(gate) * up), where in every
+ *                                 128-column tile of the weight the first 64 columns are gate columns
+ *                                 and the last 64 the up columns of the same 64 outputs (N % 128 == 0).
+ * The fp16 modes need a plan without partial sums: pass split_k = 1. */
+#define WMMA_OPS_W4_OUT_F32 0
+#define WMMA_OPS_W4_OUT_F16 1
+#define WMMA_OPS_W4_OUT_F16_SILU_MUL 2
+int wmma_ops_w4a16_gemm_ex(const void* A, const void* qweight, const void* scales, void* C, int M, int N,
+                           int K, int group_size, int split_k, int out_mode, float alpha, void* workspace,
+                           size_t workspace_bytes, int* status, void* stream);
+
 /* Flash-attention forward: O = softmax(scale * Q K^T [+ causal mask]) V per (b,h).
  * Q, K, V, O are [B,H,S,D] fp16 contiguous; the signature documented in the reference's
  * README.md:221-251 (its implementation is not in the reference tree).

@@ -24,19 +24,19 @@ def test_layer_full_shapes_few_tokens(cuda, world):
     for r in range(world):
         local = {k: (c.to(cuda), s.to(cuda)) for k, (c, s) in sharded.shard_layer_weights(weights, r, world).items()}
         layers.append(sharded.ShardedDecoderLinears(local, world=1))
-    # emulate the two all-reduces by summing the ranks' partials
+    # emulate the two all-reduces by summing the ranks' partials (same fused calls the layer makes)
+    G = sharded.GLUE_SCALE
     attn = None
     for layer in layers:
-        qkv = layer._matmul(xd, "qkv")
-        part = layer._matmul((qkv[:, :layer.q_cols] * sharded.GLUE_SCALE).half(), "o")
+        qkv16 = layer._w4(xd, "qkv", out_dtype=torch.float16, alpha=G)
+        part = layer._w4(qkv16[:, :layer.q_cols].contiguous(), "o")
         attn = part if attn is None else attn + part
     mlp = None
-    h = (attn * sharded.GLUE_SCALE).half()
+    h = (attn * G).half()
     for layer in layers:
-        gu = layer._matmul(h, "gate_up")
-        f = layer.ffn_local
-        act = (torch.nn.functional.silu(gu[:, :f]) * gu[:, f:] * sharded.GLUE_SCALE).half()
-        part = layer._matmul(act, "down")
+        act = layer._w4(h, "gate_up", epilogue="silu_mul", alpha=G)
+        assert act.shape == (192, layer.ffn_local) and act.dtype == torch.float16
+        part = layer._w4(act, "down")
         mlp = part if mlp is None else mlp + part
     torch.cuda.synchronize()
     w.check_status()

@@ -137,6 +137,35 @@ def test_fused_matches_dequant_then_dense_gemm(cuda):
     assert og.rel_frobenius(fused, two_pass.cpu()) < 1e-5
 
 
+@pytest.mark.parametrize("M", [5, 100, 300])
+def test_fused_fp16_output(cuda, M):
+    codes, scales = int4.seeded_w4(512, 264, 128, seed=13)
+    A, _ = og.seeded_ab(M, 8, 512, seed=14)
+    q, sc = w.int4_prepack(codes.to(cuda), scales.to(cuda), 128)
+    out = w.matmul_w4a16(A.to(cuda), q, sc, 128, out_dtype=torch.float16, alpha=0.25)
+    _sync_ok()
+    ref = (int4.w4a16_ref(A, codes, scales, 128) * 0.25)
+    assert out.dtype == torch.float16 and tuple(out.shape) == (M, 264)
+    # same accumulators, one rounding to fp16: at most one fp16 ulp from the rounded oracle
+    assert og.rel_frobenius(out.float(), ref) < 1e-3
+    assert (out.cpu().float() - ref.half().float()).abs().max().item() <= 2 ** -10 * ref.abs().max().item()
+
+
+@pytest.mark.parametrize("M", [3, 70, 200, 600])
+def test_fused_silu_mul_output(cuda, M):
+    K, F = 512, 384
+    codes, scales = int4.seeded_w4(K, 2 * F, 128, seed=15)     # columns: gate | up
+    A, _ = og.seeded_ab(M, 8, K, seed=16)
+    ci, si = w.interleave_gate_up(codes.to(cuda), scales.to(cuda))
+    q, sc = w.int4_prepack(ci, si, 128)
+    out = w.matmul_w4a16(A.to(cuda), q, sc, 128, epilogue="silu_mul", alpha=0.25)
+    _sync_ok()
+    gu = int4.w4a16_ref(A, codes, scales, 128)
+    ref = torch.nn.functional.silu(gu[:, :F]) * gu[:, F:] * 0.25
+    assert out.dtype == torch.float16 and tuple(out.shape) == (M, F)
+    assert og.rel_frobenius(out.float(), ref) < 2e-3    # fp16 output rounding + fast exp
+
+
 def test_w4a16_errors(cuda):
     codes, scales = int4.seeded_w4(256, 128, 128, seed=8)
     q, sc = w.int4_prepack(codes.to(cuda), scales.to(cuda), 128)
@@ -152,3 +181,7 @@ def test_w4a16_errors(cuda):
     with pytest.raises(RuntimeError, match="scales do not match"):
         w.matmul_w4a16(A, q, sc, 64)
     assert w.matmul_w4a16(A[:0], q, sc, 128).shape == (0, 128)
+    with pytest.raises(RuntimeError, match="epilogue must be"):
+        w.matmul_w4a16(A, q, sc, 128, epilogue="gelu")
+    with pytest.raises(RuntimeError, match="alpha is only applied"):
+        w.matmul_w4a16(A, q, sc, 128, alpha=2.0)

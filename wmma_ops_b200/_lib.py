@@ -46,6 +46,8 @@ SIGNATURES = {
     "wmma_ops_w4a16_select_split": (_c_int, [_c_int, _c_int, _c_int, _c_int]),
     "wmma_ops_w4a16_gemm": (_c_int, [_vp, _vp, _vp, _vp, _c_int, _c_int, _c_int, _c_int, _c_int, _vp,
                                      _c_size_t, _vp, _vp]),
+    "wmma_ops_w4a16_gemm_ex": (_c_int, [_vp, _vp, _vp, _vp, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_float,
+                                        _vp, _c_size_t, _vp, _vp]),
     "wmma_ops_fmha_fwd": (_c_int, [_vp, _vp, _vp, _vp, _c_int, _c_int, _c_int, _c_int, _c_float, _c_int,
                                    _vp, _vp]),
 }

@@ -20,7 +20,10 @@ constexpr int W4_DQ_WARPS = 8;     // each dequant warp expands a whole 4 KB blo
 struct W4Params {
     const uint32_t* qweight;
     const __half* scales;
-    float* C;
+    float* C;          // fp32 output (out_mode 0)
+    __half* C16;       // fp16 output (out_mode 1: [M,N]; out_mode 2: [M,N/2])
+    int out_mode;      // 0: C = acc; 1: C16 = half(alpha*acc); 2: C16 = half(alpha*silu(gate)*up)
+    float alpha;
     float* partials;   // [tiles][split][BT][128]
     int* counters;     // [tiles]
     int M, N, K;

@@ -38,7 +38,7 @@ struct W4Cfg {
     // then never be more than one phase away from the barrier's state.
     static constexpr int S = (BT >= 256) ? 4 : (BT >= 64) ? 6 : 8;
     static constexpr int R = (BT >= 256) ? 4 : (BT >= 128) ? 6 : (BT >= 64) ? 12 : (BT >= 32) ? 8 : 16;
-    static_assert(S * S_STAGE + R * W4_SLOT_BYTES + 1024 + 512 <= 232448, "shared memory budget");
+    static_assert(S * S_STAGE + R * W4_SLOT_BYTES + 1024 + 512 + 32 * 64 * 4 <= 232448, "shared memory budget");
     static constexpr int DQ = S;
     static_assert(R % S == 0 && DQ <= W4_DQ_WARPS, "ring sizes must nest");
     // WM (worker-MMA, decode): every worker accumulates into its own BT columns, two sets
@@ -46,7 +46,8 @@ struct W4Cfg {
     static constexpr int TMEM_NEED = 2 * ACCS * BT;
     static constexpr int TMEM_COLS = TMEM_NEED <= 32 ? 32 : TMEM_NEED <= 64 ? 64 : TMEM_NEED <= 128 ? 128 : TMEM_NEED <= 256 ? 256 : 512;
     static_assert(TMEM_NEED <= 512, "TMEM budget");
-    static constexpr int SMEM_BYTES = S * S_STAGE + R * W4_SLOT_BYTES + 1024 + 512;
+    static constexpr int STAGE_OUT_BYTES = 32 * 64 * 4;  // silu(gate)*up hand-over between epilogue warps
+    static constexpr int SMEM_BYTES = S * S_STAGE + R * W4_SLOT_BYTES + 1024 + 512 + STAGE_OUT_BYTES;
 };
 
 
@@ -75,6 +76,7 @@ w4a16_gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_const
     auto acc_empty = [&](int b) { return bar_base + 8u * (3 * Cfg::S + 2 * Cfg::R + 2 + b); };
     const uint32_t tmem_slot = bar_base + 8u * (3 * Cfg::S + 2 * Cfg::R + 4);
     const uint32_t flag_slot = tmem_slot + 8u;
+    const uint32_t out_stage = bar_base + 512u;  // 8 KB, used by the fused silu(gate)*up epilogue
     static_assert(8 * (3 * Cfg::S + 2 * Cfg::R + 6) <= 512, "barrier area too small");
 
     const int warp = threadIdx.x >> 5;
@@ -308,12 +310,49 @@ w4a16_gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_const
                 if (part != nullptr) {
 #pragma unroll
                     for (int j = 0; j < CH; ++j) part[(c * CH + j) * 128 + row] = __uint_as_float(v[j]);
-                } else if (n < p.N) {
+                } else if (p.out_mode == 0) {
+                    if (n < p.N) {
 #pragma unroll
-                    for (int j = 0; j < CH; ++j) {
-                        const int t = t0 + c * CH + j;
-                        if (t < p.M) p.C[static_cast<size_t>(t) * p.N + n] = __uint_as_float(v[j]);
+                        for (int j = 0; j < CH; ++j) {
+                            const int t = t0 + c * CH + j;
+                            if (t < p.M) p.C[static_cast<size_t>(t) * p.N + n] = __uint_as_float(v[j]);
+                        }
                     }
+                } else if (p.out_mode == 1) {
+                    if (n < p.N) {
+#pragma unroll
+                        for (int j = 0; j < CH; ++j) {
+                            const int t = t0 + c * CH + j;
+                            if (t < p.M)
+                                p.C16[static_cast<size_t>(t) * p.N + n] = __float2half_rn(p.alpha * __uint_as_float(v[j]));
+                        }
+                    }
+                } else {
+                    // Fused gate/up: the tile's rows 0..63 are gate columns and rows 64..127 the up
+                    // columns of the same 64 outputs. The up warps pass their values through shared
+                    // memory ([token][row] so that lanes hit consecutive banks); the gate warps
+                    // compute alpha * silu(gate) * up and store fp16.
+                    if (row >= 64) {
+#pragma unroll
+                        for (int j = 0; j < CH; ++j)
+                            asm volatile("st.shared.u32 [%0], %1;" ::"r"(out_stage + (j * 64 + row - 64) * 4), "r"(v[j])
+                                         : "memory");
+                    }
+                    named_barrier_sync(3, 128);
+                    if (row < 64) {
+                        const int f = nt * 64 + row;
+                        const int ldo = p.N / 2;
+#pragma unroll
+                        for (int j = 0; j < CH; ++j) {
+                            uint32_t ub;
+                            asm volatile("ld.shared.u32 %0, [%1];" : "=r"(ub) : "r"(out_stage + (j * 64 + row) * 4) : "memory");
+                            const float gte = __uint_as_float(v[j]);
+                            const float act = p.alpha * (gte / (1.f + __expf(-gte))) * __uint_as_float(ub);
+                            const int t = t0 + c * CH + j;
+                            if (t < p.M && f < ldo) p.C16[static_cast<size_t>(t) * ldo + f] = __float2half_rn(act);
+                        }
+                    }
+                    named_barrier_sync(3, 128);
                 }
             }
             tc_fence_before_sync();
@@ -569,7 +608,18 @@ extern "C" size_t wmma_ops_w4a16_workspace_bytes(int M, int N, int K, int split_
 extern "C" int wmma_ops_w4a16_gemm(const void* A, const void* qweight, const void* scales, void* C, int M,
                                    int N, int K, int group_size, int split_k, void* workspace,
                                    size_t workspace_bytes, int* status, void* stream_) {
+    return wmma_ops_w4a16_gemm_ex(A, qweight, scales, C, M, N, K, group_size, split_k, WMMA_OPS_W4_OUT_F32, 1.0f,
+                                  workspace, workspace_bytes, status, stream_);
+}
+
+extern "C" int wmma_ops_w4a16_gemm_ex(const void* A, const void* qweight, const void* scales, void* C, int M,
+                                      int N, int K, int group_size, int split_k, int out_mode, float alpha,
+                                      void* workspace, size_t workspace_bytes, int* status, void* stream_) {
     using namespace wb;
+    WB_REQUIRE(out_mode >= WMMA_OPS_W4_OUT_F32 && out_mode <= WMMA_OPS_W4_OUT_F16_SILU_MUL, WMMA_OPS_ERR_INVALID,
+               "w4a16: unknown out_mode %d", out_mode);
+    WB_REQUIRE(out_mode != WMMA_OPS_W4_OUT_F16_SILU_MUL || N % 128 == 0, WMMA_OPS_ERR_INVALID,
+               "w4a16: the fused gate/up epilogue needs N to be a multiple of 128 (got N=%d)", N);
     cudaStream_t stream = static_cast<cudaStream_t>(stream_);
     WB_REQUIRE(M >= 0, WMMA_OPS_ERR_INVALID, "w4a16: negative M");
     int rc = check_w4_shape(K, N);
@@ -592,6 +642,9 @@ extern "C" int wmma_ops_w4a16_gemm(const void* A, const void* qweight, const voi
     p.qweight = static_cast<const uint32_t*>(qweight);
     p.scales = static_cast<const __half*>(scales);
     p.C = static_cast<float*>(C);
+    p.C16 = static_cast<__half*>(C);
+    p.out_mode = out_mode;
+    p.alpha = alpha;
     p.M = M;
     p.N = N;
     p.K = K;
@@ -605,6 +658,8 @@ extern "C" int wmma_ops_w4a16_gemm(const void* A, const void* qweight, const voi
     p.max_slices = plan.max_slices;
     p.partials = nullptr;
     p.counters = nullptr;
+    WB_REQUIRE(out_mode == WMMA_OPS_W4_OUT_F32 || !plan.partials(), WMMA_OPS_ERR_INVALID,
+               "w4a16: fp16 / fused outputs need a plan without partial sums (pass split_k = 1)");
     if (plan.partials()) {
         const size_t need = plan.workspace_bytes();
         WB_REQUIRE(workspace != nullptr && workspace_bytes >= need, WMMA_OPS_ERR_WORKSPACE,

@@ -76,15 +76,37 @@ def int4_dequant(qweight: torch.Tensor, scales: torch.Tensor, group_size: int = 
     return out
 
 
+OUT_F32, OUT_F16, OUT_F16_SILU_MUL = 0, 1, 2
+
+
+def interleave_gate_up(codes: torch.Tensor, scales: torch.Tensor) -> Tuple[torch.Tensor, torch.Tensor]:
+    """Reorders the columns of a [K, 2F] gate|up weight (gate columns first, then up columns) so that
+    every 128-column tile holds 64 gate columns followed by the 64 up columns of the same outputs,
+    the layout the fused silu(gate) * up epilogue of matmul_w4a16 expects. F must be a multiple of 64."""
+    K, N2 = codes.shape
+    F = N2 // 2
+    _require(N2 % 2 == 0 and F % 64 == 0, "gate/up width must be a multiple of 64")
+    idx = torch.arange(F, device=codes.device).view(F // 64, 1, 64)
+    order = torch.cat([idx, idx + F], dim=1).reshape(-1)
+    return codes[:, order].contiguous(), scales[:, order].contiguous()
+
+
 def matmul_w4a16(A: torch.Tensor, qweight: torch.Tensor, scales: torch.Tensor, group_size: int = 128,
-                 split_k: int = 0) -> torch.Tensor:
-    """C fp32 [M,N] = A fp16 [M,K] @ dequant(qweight, scales); the weights are expanded to fp16
-    inside the kernel's shared memory. split_k=0 lets the library choose."""
+                 split_k: int = 0, out_dtype: torch.dtype = torch.float32, alpha: float = 1.0,
+                 epilogue: str = "none") -> torch.Tensor:
+    """C [M,N] = A fp16 [M,K] @ dequant(qweight, scales); the weights are expanded to fp16 inside the
+    kernel's shared memory. split_k=0 lets the library choose.
+
+    out_dtype=torch.float32 (default) returns the fp32 accumulators. out_dtype=torch.float16 returns
+    half(alpha * acc). epilogue="silu_mul" (weights prepared with interleave_gate_up) returns
+    half(alpha * silu(gate) * up) of shape [M, N/2]."""
     _require(A.is_cuda and qweight.is_cuda and scales.is_cuda, "Inputs must be CUDA tensors")
     _require(A.device == qweight.device and A.device == scales.device, "Inputs must be on same device")
     _require(A.dtype == torch.float16, "Inputs must be float16")
     _require(scales.dtype == torch.float16 and scales.dim() == 2, "scales must be float16 [K/group_size, N]")
     _require(A.dim() == 2, "Inputs must be 2D")
+    _require(epilogue in ("none", "silu_mul"), "epilogue must be 'none' or 'silu_mul'")
+    _require(out_dtype in (torch.float32, torch.float16), "out_dtype must be float32 or float16")
     N = scales.size(1)
     K, N = _qshape(qweight, N)
     _require(A.size(1) == K, "Inner dimensions must match")
@@ -95,17 +117,27 @@ def matmul_w4a16(A: torch.Tensor, qweight: torch.Tensor, scales: torch.Tensor, g
     M = A.size(0)
     dev = A.device
     lib = _lib.load()
-    C = torch.empty((M, N), dtype=torch.float32, device=dev)
+    if epilogue == "silu_mul":
+        _require(N % 128 == 0, "the fused gate/up epilogue needs N to be a multiple of 128")
+        mode, C = OUT_F16_SILU_MUL, torch.empty((M, N // 2), dtype=torch.float16, device=dev)
+    elif out_dtype == torch.float16:
+        mode, C = OUT_F16, torch.empty((M, N), dtype=torch.float16, device=dev)
+    else:
+        _require(float(alpha) == 1.0, "alpha is only applied to float16 outputs")
+        mode, C = OUT_F32, torch.empty((M, N), dtype=torch.float32, device=dev)
     if M == 0:
         return C
+    if mode != OUT_F32 and split_k == 0:
+        split_k = 1   # fp16 outputs are written straight from the accumulators: no partial sums
     with torch.cuda.device(dev):
         ws_ptr, ws_bytes = None, 0
         need = lib.wmma_ops_w4a16_workspace_bytes(M, N, K, split_k)   # split_k = 0: the library's own plan
         if need > 0:
             ws = _workspace(dev, need, zero_init=True)
             ws_ptr, ws_bytes = ws.data_ptr(), ws.numel()
-        rc = lib.wmma_ops_w4a16_gemm(A.data_ptr(), qweight.data_ptr(), scales.data_ptr(), C.data_ptr(), M, N, K,
-                                     group_size, split_k, ws_ptr, ws_bytes, _status_word(dev).data_ptr(), _stream(dev))
+        rc = lib.wmma_ops_w4a16_gemm_ex(A.data_ptr(), qweight.data_ptr(), scales.data_ptr(), C.data_ptr(), M, N, K,
+                                        group_size, split_k, mode, float(alpha), ws_ptr, ws_bytes,
+                                        _status_word(dev).data_ptr(), _stream(dev))
         _lib.check(rc)
         _post(dev)
     return C

@@ -100,11 +100,17 @@ class ShardedDecoderLinears:
         self.chunks = max(1, chunks)
         self.q_cols = local_weights["qkv"][0].shape[1] // 3
         self.ffn_local = local_weights["gate_up"][0].shape[1] // 2
+        self.fused = matmul is None
         if matmul is None:
-            from .quant import int4_prepack, matmul_w4a16
-            packed = {k: int4_prepack(c, s, group) for k, (c, s) in local_weights.items()}
-            matmul = lambda x, name: matmul_w4a16(x, packed[name][0], packed[name][1], group)  # noqa: E731
+            # Product path: prepacked shards, fused output stages (fp16 activations written by the
+            # GEMM epilogue, silu(gate) * up inside the gate/up GEMM).
+            from .quant import int4_prepack, interleave_gate_up, matmul_w4a16
+            prepared = dict(local_weights)
+            prepared["gate_up"] = interleave_gate_up(*local_weights["gate_up"])
+            packed = {k: int4_prepack(c, s, group) for k, (c, s) in prepared.items()}
             self.packed = packed
+            self._w4 = lambda x, name, **kw: matmul_w4a16(x, packed[name][0], packed[name][1], group, **kw)  # noqa: E731
+            matmul = lambda x, name: self._w4(x, name)  # noqa: E731
         self._matmul = matmul
         if all_reduce is None:
             all_reduce = self._dist_all_reduce
@@ -140,6 +146,8 @@ class ShardedDecoderLinears:
         """x fp16 [T, hidden] (replicated) -> (attn_out, mlp_out), both [T, hidden], replicated,
         in reduce_dtype. The glue is the oracle's: O's input is this rank's slice of the Q section
         of the QKV output; the MLP input is attn_out; act = silu(gate) * up; each scaled by GLUE_SCALE, fp16 between GEMMs."""
+        if self.fused:
+            return self._forward_fused(x)
         qkv = self._matmul(x, "qkv")
         o_in = (qkv[:, :self.q_cols] * GLUE_SCALE).to(torch.float16)
         attn_out = self._row_parallel(o_in, "o")
@@ -147,6 +155,20 @@ class ShardedDecoderLinears:
         gu = self._matmul(h, "gate_up")
         f = self.ffn_local
         act = (torch.nn.functional.silu(gu[:, :f]) * gu[:, f:] * GLUE_SCALE).to(torch.float16)
+        mlp_out = self._row_parallel(act, "down")
+        return attn_out, mlp_out
+
+    def _forward_fused(self, x: torch.Tensor) -> Tuple[torch.Tensor, torch.Tensor]:
+        """Same arithmetic with the glue inside the GEMM epilogues: QKV writes half(GLUE_SCALE * acc),
+        gate/up writes half(GLUE_SCALE * silu(gate) * up); only the slice copy and the scaling of the
+        all-reduced attention output remain as separate (small) kernels."""
+        out_dt = self.reduce_dtype
+        qkv16 = self._w4(x, "qkv", out_dtype=torch.float16, alpha=GLUE_SCALE)
+        o_in = qkv16[:, :self.q_cols].contiguous()
+        self._matmul = lambda a, name: self._w4(a, name, out_dtype=out_dt)  # noqa: E731
+        attn_out = self._row_parallel(o_in, "o")
+        h = (attn_out * GLUE_SCALE).to(torch.float16)
+        act = self._w4(h, "gate_up", epilogue="silu_mul", alpha=GLUE_SCALE)
         mlp_out = self._row_parallel(act, "down")
         return attn_out, mlp_out
 
