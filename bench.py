@@ -289,7 +289,8 @@ def measure_layer(w, dev, rank, world, steps):
     del full
     x = torch.randn(tokens, 4096, generator=gen, device=dev).half()
     out = {}
-    for label, rdt, chunks in (("fp32_reduce", torch.float32, 1), ("fp16_reduce_chunked", torch.float16, 4)):
+    for label, rdt, chunks in (("fp32_reduce", torch.float32, 1), ("fp16_reduce", torch.float16, 1),
+                               ("fp16_reduce_2chunks", torch.float16, 2)):
         if world == 1 and label != "fp32_reduce":
             continue
         layer = sharded.ShardedDecoderLinears(local, world=world, reduce_dtype=rdt, chunks=chunks)
@@ -322,6 +323,8 @@ def run_ours(args):
     dev = torch.device("cuda", local_rank)
     torch.cuda.set_device(dev)
     if world > 1:
+        # stdout carries exactly one JSON line: keep NCCL's version banner off it
+        os.environ["NCCL_DEBUG"] = "WARN"
         import torch.distributed as dist
         dist.init_process_group("nccl", device_id=dev)
     peaks = load_peaks()
