@@ -8,11 +8,12 @@
 // of 128 with an online softmax:
 //   warp 0      TMA producer: Q once, then K and V tiles into two-stage rings
 //   warp 1      TMEM owner and MMA issuer: S = Q K^T (fp32, TMEM), O += P V (fp32, TMEM)
-//   warps 2..5  softmax: one query row per thread; read S from TMEM, keep the running max and
-//               sum, write P (fp16) into 128-byte-swizzled shared memory as the A operand of
-//               P V, rescale O in TMEM when the max moved, and at the end store O / l as fp16.
-// Two S accumulators and two P buffers let Q K^T of tile i+1 run on the tensor cores while the
-// softmax warps work on tile i. K is a K-major operand; V, read as [kv, d] with d contiguous,
+//   warps 2..9  softmax: two warps per TMEM lane quadrant, each thread one query row and half of
+//               the tile's keys; read S from TMEM, keep the running max and sum, write P (fp16)
+//               back into tensor memory over S, from where P V reads it as its A operand,
+//               rescale O in TMEM when the max moved, and at the end store O / l as fp16.
+// Two S accumulators let Q K^T of tile i+1 run on the tensor cores while the softmax warps
+// work on tile i. K is a K-major operand; V, read as [kv, d] with d contiguous,
 // is an MN-major operand, so neither is transposed.
 #include "host_common.cuh"
 #include "ptx.cuh"
@@ -21,15 +22,15 @@ namespace wb {
 
 constexpr int FA_BM = 128;  // query rows per CTA
 constexpr int FA_BN = 128;  // keys per tile
-constexpr int FA_THREADS = 192;
+constexpr int FA_THREADS = 320;  // warp 0 producer, warp 1 MMA, warps 2..9 softmax
 
 template <int D>
 struct FaCfg {
     static constexpr int DB = D / 64;                   // 64-wide head-dim blocks
     static constexpr int TILE_BYTES = 128 * D * 2;      // Q, K or V tile
     static constexpr int BOX_BYTES = 128 * 64 * 2;      // one [128 rows x 64 halves] box
-    static constexpr int P_BYTES = FA_BM * FA_BN * 2;   // one P buffer
-    static constexpr int SMEM_BYTES = 5 * TILE_BYTES + 2 * P_BYTES + 1024 + 256;
+    static constexpr int XCHG_BYTES = 2 * FA_BM * 4;    // row maxima / sums passed between the two column halves
+    static constexpr int SMEM_BYTES = 5 * TILE_BYTES + 1024 + 256 + XCHG_BYTES;
     static constexpr int TMEM_COLS = 512;
     static constexpr int S_COL0 = 0, S_COL1 = 128, O_COL = 256;
 };
@@ -71,8 +72,8 @@ fmha_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
     const uint32_t q_smem = smem_base;
     auto k_smem = [&](int s) { return smem_base + (1 + s) * Cfg::TILE_BYTES; };
     auto v_smem = [&](int s) { return smem_base + (3 + s) * Cfg::TILE_BYTES; };
-    auto p_smem = [&](int s) { return smem_base + 5 * Cfg::TILE_BYTES + s * Cfg::P_BYTES; };
-    const uint32_t bar_base = smem_base + 5 * Cfg::TILE_BYTES + 2 * Cfg::P_BYTES;
+    const uint32_t bar_base = smem_base + 5 * Cfg::TILE_BYTES;
+    const uint32_t xchg = bar_base + 256u;  // [2 halves][128 rows] floats
     const uint32_t q_full = bar_base;
     auto k_full = [&](int s) { return bar_base + 8u * (1 + s); };
     auto k_empty = [&](int s) { return bar_base + 8u * (3 + s); };
@@ -103,8 +104,8 @@ fmha_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
             mbar_init(v_full(s), 1);
             mbar_init(v_empty(s), 1);
             mbar_init(s_full(s), 1);
-            mbar_init(s_empty(s), 128);
-            mbar_init(p_ready(s), 128);
+            mbar_init(s_empty(s), 1);  // unused: S buffers are recycled in MMA issue order
+            mbar_init(p_ready(s), 256);
         }
         mbar_init(pv_done, 1);
         fence_barrier_init();
@@ -168,12 +169,12 @@ fmha_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
                 tc_fence_after_sync();
 #pragma unroll
                 for (int kk = 0; kk < FA_BN / 16; ++kk) {
-                    // P: K-major, 64 keys per 16 KB block, 32 bytes per 16 keys inside a block
-                    const uint64_t a_desc =
-                        make_smem_desc_sw128(p_smem(s) + (kk >> 2) * Cfg::BOX_BYTES + (kk & 3) * 32, 16, 1024);
+                    // P (fp16, written by the softmax warps over the first 64 columns of S buffer s) is
+                    // the A operand straight from tensor memory: 16 keys = 8 columns per MMA.
                     // V: MN-major, 16 keys = 2048 bytes further; 64-wide d blocks BOX_BYTES apart
                     const uint64_t b_desc = make_smem_desc_sw128(v_smem(s) + kk * 2048, Cfg::BOX_BYTES, 1024);
-                    umma_f16(tmem_base + Cfg::O_COL, a_desc, b_desc, idesc_o, (i > 0 || kk > 0) ? 1u : 0u);
+                    umma_f16_ts(tmem_base + Cfg::O_COL, tmem_base + (s ? Cfg::S_COL1 : Cfg::S_COL0) + kk * 8, b_desc,
+                                idesc_o, (i > 0 || kk > 0) ? 1u : 0u);
                 }
                 umma_commit(v_empty(s));
                 umma_commit(pv_done);
@@ -182,7 +183,7 @@ fmha_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
             for (int i = 0; ok && i < n_tiles; ++i) {
                 const int s = i & 1;
                 const uint32_t ph = (i >> 1) & 1;
-                if (!mbar_wait(k_full(s), ph) || !mbar_wait(s_empty(s), ph ^ 1u)) {
+                if (!mbar_wait(k_full(s), ph)) {
                     fa_report(p.status, 1, i);
                     ok = false;
                     break;
@@ -203,14 +204,19 @@ fmha_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
             if (ok && n_tiles > 0) issue_pv(n_tiles - 1);
         }
     } else {
-        // ------------------------------------------------------------ softmax warps (2..5)
+        // ------------------------------------------------------------ softmax warps (2..9)
+        // Two warps share each TMEM lane quadrant: warp (quad, half) owns the query rows
+        // 32*quad .. 32*quad+31 and the key columns 64*half .. 64*half+63 of every S tile, and the
+        // head-dim columns D/2*half .. of O. The halves exchange their row maxima through shared
+        // memory once per tile; the row sums are kept per half and added at the end.
         const int quad = warp & 3;
+        const int half = (warp - 2) >> 2;
         const int row = quad * 32 + lane;
         const int q = q0 + row;
         const uint32_t lane_addr = static_cast<uint32_t>(quad * 32) << 16;
         const float sl2 = p.scale_log2;
-        float m_run = -INFINITY;  // running max of scale*log2e*s
-        float l_run = 0.f;        // running sum of exp2(scale*log2e*s - m_run)
+        float m_run = -INFINITY;  // running max of scale*log2e*s over both halves
+        float l_run = 0.f;        // running sum of exp2(.) over this half's columns
         bool ok = true;
         for (int i = 0; ok && i < n_tiles; ++i) {
             const int s = i & 1;
@@ -222,61 +228,55 @@ fmha_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
             }
             tc_fence_after_sync();
             const uint32_t s_addr = tmem_base + (s ? Cfg::S_COL1 : Cfg::S_COL0) + lane_addr;
-            const int kv0 = i * FA_BN;
-            const bool need_mask = (p.causal && kv0 + FA_BN - 1 > q0) || (kv0 + FA_BN > p.S);
+            const int kv0 = i * FA_BN + half * 64;
+            const bool need_mask = (p.causal && i * FA_BN + FA_BN - 1 > q0) || (i * FA_BN + FA_BN > p.S);
             const int col_limit = p.causal ? min(p.S - 1, q) : p.S - 1;  // last visible key
 
-            // pass 1: row maximum
-            float mx = -INFINITY;
-#pragma unroll 1
-            for (int c = 0; c < FA_BN / 32; ++c) {
+            // this half's 64 scores, scaled, kept in registers
+            float x[64];
+            {
                 uint32_t v[32];
-                tmem_ld_32x32b_x32(s_addr + c * 32, v);
+                tmem_ld_32x32b_x32(s_addr + half * 64, v);
                 tmem_wait_ld();
 #pragma unroll
-                for (int j = 0; j < 32; ++j) {
-                    float x = __uint_as_float(v[j]) * sl2;
-                    if (need_mask && kv0 + c * 32 + j > col_limit) x = -INFINITY;
-                    mx = fmaxf(mx, x);
-                }
+                for (int j = 0; j < 32; ++j) x[j] = __uint_as_float(v[j]) * sl2;
+                tmem_ld_32x32b_x32(s_addr + half * 64 + 32, v);
+                tmem_wait_ld();
+#pragma unroll
+                for (int j = 0; j < 32; ++j) x[32 + j] = __uint_as_float(v[j]) * sl2;
             }
-            const float m_new = fmaxf(m_run, mx);
+            float mx = -INFINITY;
+#pragma unroll
+            for (int j = 0; j < 64; ++j) {
+                if (need_mask && kv0 + j > col_limit) x[j] = -INFINITY;
+                mx = fmaxf(mx, x[j]);
+            }
+            // exchange the row maximum with the other half
+            asm volatile("st.shared.f32 [%0], %1;" ::"r"(xchg + (half * FA_BM + row) * 4), "f"(mx) : "memory");
+            named_barrier_sync(1, 256);
+            float mx_other;
+            asm volatile("ld.shared.f32 %0, [%1];" : "=f"(mx_other) : "r"(xchg + ((half ^ 1) * FA_BM + row) * 4) : "memory");
+            const float m_new = fmaxf(m_run, fmaxf(mx, mx_other));
             const float m_safe = (m_new == -INFINITY) ? 0.f : m_new;
             const float alpha = fast_exp2(m_run - m_safe);
 
-            // pass 2: probabilities -> fp16 P tile (K-major, 128-byte swizzle), row sum
+            // probabilities -> fp16, written over the start of the S buffer (both halves have read
+            // all of S before the barrier above): columns 32*half .. 32*half+31 hold this half's keys
             float sum = 0.f;
-            const uint32_t p_base = p_smem(s);
-#pragma unroll 1
-            for (int c = 0; c < FA_BN / 32; ++c) {
-                uint32_t v[32];
-                tmem_ld_32x32b_x32(s_addr + c * 32, v);
-                tmem_wait_ld();
-                float e[32];
+            uint32_t pk[32];
 #pragma unroll
-                for (int j = 0; j < 32; ++j) {
-                    float x = fmaf(__uint_as_float(v[j]), sl2, -m_safe);
-                    if (need_mask && kv0 + c * 32 + j > col_limit) x = -INFINITY;
-                    e[j] = fast_exp2(x);
-                    sum += e[j];
-                }
-#pragma unroll
-                for (int g = 0; g < 4; ++g) {
-                    const int col = c * 32 + g * 8;  // key index inside the tile
-                    const uint32_t dst = p_base + (col >> 6) * Cfg::BOX_BYTES + sw128_offset(row, (col & 63) >> 3);
-                    asm volatile("st.shared.v4.u32 [%0], {%1, %2, %3, %4};" ::"r"(dst),
-                                 "r"(pack_half2(e[g * 8 + 0], e[g * 8 + 1])), "r"(pack_half2(e[g * 8 + 2], e[g * 8 + 3])),
-                                 "r"(pack_half2(e[g * 8 + 4], e[g * 8 + 5])), "r"(pack_half2(e[g * 8 + 6], e[g * 8 + 7]))
-                                 : "memory");
-                }
+            for (int j = 0; j < 32; ++j) {
+                const float e0 = fast_exp2(x[2 * j] - m_safe);
+                const float e1 = fast_exp2(x[2 * j + 1] - m_safe);
+                sum += e0 + e1;
+                pk[j] = pack_half2(e0, e1);
             }
-            tc_fence_before_sync();
-            mbar_arrive(s_empty(s));
+            tmem_st_32x32b_x32(s_addr + half * 32, pk);
             l_run = l_run * alpha + sum;
             m_run = m_new;
 
             if (i > 0) {
-                // O holds the sum through tile i-1; bring it to the new maximum before P_i V_i
+                // O holds the sum through tile i-1; bring this half's columns to the new maximum
                 if (!mbar_wait(pv_done, (i - 1) & 1)) {
                     fa_report(p.status, 2, 1000 + i);
                     ok = false;
@@ -284,9 +284,9 @@ fmha_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
                 }
                 tc_fence_after_sync();
                 if (__any_sync(0xffffffffu, alpha != 1.f)) {
-                    const uint32_t o_addr = tmem_base + Cfg::O_COL + lane_addr;
+                    const uint32_t o_addr = tmem_base + Cfg::O_COL + lane_addr + half * (D / 2);
 #pragma unroll 1
-                    for (int c = 0; c < D / 32; ++c) {
+                    for (int c = 0; c < D / 64; ++c) {
                         uint32_t v[32];
                         tmem_ld_32x32b_x32(o_addr + c * 32, v);
                         tmem_wait_ld();
@@ -294,36 +294,44 @@ fmha_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
                         for (int j = 0; j < 32; ++j) v[j] = __float_as_uint(__uint_as_float(v[j]) * alpha);
                         tmem_st_32x32b_x32(o_addr + c * 32, v);
                     }
-                    tmem_wait_st();
                 }
             }
-            fence_proxy_async_smem();
+            tmem_wait_st();
             tc_fence_before_sync();
             mbar_arrive(p_ready(s));
+            named_barrier_sync(1, 256);  // the exchange slots are reused by the next tile
         }
         if (ok) {
             if (!mbar_wait(pv_done, (n_tiles - 1) & 1)) {
                 fa_report(p.status, 2, -1);
-            } else {
-                tc_fence_after_sync();
-                const float inv = (l_run > 0.f) ? 1.f / l_run : 0.f;
-                const uint32_t o_addr = tmem_base + Cfg::O_COL + lane_addr;
-                __half* out = p.O + (static_cast<size_t>(bh) * p.S + q) * D;
+                ok = false;
+            }
+        }
+        // total row sum = sum of the two halves
+        asm volatile("st.shared.f32 [%0], %1;" ::"r"(xchg + (half * FA_BM + row) * 4), "f"(l_run) : "memory");
+        named_barrier_sync(1, 256);
+        if (ok) {
+            float l_other;
+            asm volatile("ld.shared.f32 %0, [%1];" : "=f"(l_other) : "r"(xchg + ((half ^ 1) * FA_BM + row) * 4) : "memory");
+            tc_fence_after_sync();
+            const float l_tot = l_run + l_other;
+            const float inv = (l_tot > 0.f) ? 1.f / l_tot : 0.f;
+            const uint32_t o_addr = tmem_base + Cfg::O_COL + lane_addr + half * (D / 2);
+            __half* out = p.O + (static_cast<size_t>(bh) * p.S + q) * D + half * (D / 2);
 #pragma unroll 1
-                for (int c = 0; c < D / 32; ++c) {
-                    uint32_t v[32];
-                    tmem_ld_32x32b_x32(o_addr + c * 32, v);
-                    tmem_wait_ld();
-                    if (q < p.S) {
+            for (int c = 0; c < D / 64; ++c) {
+                uint32_t v[32];
+                tmem_ld_32x32b_x32(o_addr + c * 32, v);
+                tmem_wait_ld();
+                if (q < p.S) {
 #pragma unroll
-                        for (int g = 0; g < 4; ++g) {
-                            uint4 o;
-                            o.x = pack_half2(__uint_as_float(v[g * 8 + 0]) * inv, __uint_as_float(v[g * 8 + 1]) * inv);
-                            o.y = pack_half2(__uint_as_float(v[g * 8 + 2]) * inv, __uint_as_float(v[g * 8 + 3]) * inv);
-                            o.z = pack_half2(__uint_as_float(v[g * 8 + 4]) * inv, __uint_as_float(v[g * 8 + 5]) * inv);
-                            o.w = pack_half2(__uint_as_float(v[g * 8 + 6]) * inv, __uint_as_float(v[g * 8 + 7]) * inv);
-                            *reinterpret_cast<uint4*>(out + c * 32 + g * 8) = o;
-                        }
+                    for (int g = 0; g < 4; ++g) {
+                        uint4 o;
+                        o.x = pack_half2(__uint_as_float(v[g * 8 + 0]) * inv, __uint_as_float(v[g * 8 + 1]) * inv);
+                        o.y = pack_half2(__uint_as_float(v[g * 8 + 2]) * inv, __uint_as_float(v[g * 8 + 3]) * inv);
+                        o.z = pack_half2(__uint_as_float(v[g * 8 + 4]) * inv, __uint_as_float(v[g * 8 + 5]) * inv);
+                        o.w = pack_half2(__uint_as_float(v[g * 8 + 6]) * inv, __uint_as_float(v[g * 8 + 7]) * inv);
+                        *reinterpret_cast<uint4*>(out + c * 32 + g * 8) = o;
                     }
                 }
             }
