@@ -29,8 +29,8 @@ if str(ROOT) not in sys.path:
 
 GEMM_N = 8192
 # DRAM bytes (read + write) per 8192^3 launch of the dominant kernel, from one ncu capture
-# (profiles/gemm_f16f32_8192.md); None until captured.
-NCU_TRAFFIC_BYTES = {"gemm_8192": None}
+# (profiles/gemm_f16f32_pair_8192.md: 1.08 GB read + 0.25 GB written).
+NCU_TRAFFIC_BYTES = {"gemm_8192": 1.33e9}
 
 
 # ----------------------------------------------------------------------------- helpers
@@ -407,14 +407,36 @@ def run_ours(args):
 
 
 def run_kernel_only(args, w, dev, A, B):
-    if args.kernel_only == "gemm":
-        for _ in range(3):
-            w.matmul_adaptive(A, B)
-    elif args.kernel_only == "gemm_pair":
-        for _ in range(3):
-            w.matmul_tiled(A, B, 3)
+    """Profiling aid: a few launches of one workload on small, fixed inputs, no JSON line."""
+    gen = torch.Generator(device=dev).manual_seed(5)
+    name = args.kernel_only
+    if name == "gemm":
+        fn = lambda: w.matmul_adaptive(A, B)  # noqa: E731
+    elif name == "gemm_pair":
+        fn = lambda: w.matmul_tiled(A, B, 3)  # noqa: E731
+    elif name in ("w4a16_m1", "w4a16_m16", "w4a16_m128", "w4a16_m4096"):
+        M, K, N = int(name.split("_m")[1]), 4096, 11008
+        sets = []
+        for _ in range(6):      # 6 x 23 MB of packed weights: more than the L2
+            codes = torch.randint(0, 16, (K, N), generator=gen, device=dev, dtype=torch.uint8)
+            scales = (torch.rand(K // 128, N, generator=gen, device=dev) * 0.019 + 0.001).half()
+            sets.append(w.int4_prepack(codes, scales, 128))
+        X = torch.randn(M, K, generator=gen, device=dev).half()
+        state = {"i": 0}
+
+        def fn():
+            q, sc = sets[state["i"] % len(sets)]
+            state["i"] += 1
+            return w.matmul_w4a16(X, q, sc, 128)
+    elif name in ("fmha_s2048", "fmha_s2048_causal"):
+        Q = torch.randn(4, 32, 2048, 128, generator=gen, device=dev).half()
+        Kt = torch.randn(4, 32, 2048, 128, generator=gen, device=dev).half()
+        V = torch.randn(4, 32, 2048, 128, generator=gen, device=dev).half()
+        fn = lambda: w.flash_attention(Q, Kt, V, causal=name.endswith("causal"))  # noqa: E731
     else:
-        raise SystemExit(f"unknown --kernel-only {args.kernel_only}")
+        raise SystemExit(f"unknown --kernel-only {name}")
+    for _ in range(4):
+        fn()
     torch.cuda.synchronize()
     w.check_status(dev)
 
