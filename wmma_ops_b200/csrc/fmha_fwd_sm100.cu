@@ -220,7 +220,7 @@ fmha_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
         const int row = quad * 32 + lane;
         const int q = q0 + row;
         const uint32_t lane_addr = static_cast<uint32_t>(quad * 32) << 16;
-        const float sl2 = p.scale_log2;
+        const float sl2 = fmaxf(p.scale_log2, 1e-30f);  // > 0, so that -inf * sl2 stays -inf
         float m_run = -INFINITY;  // running max of scale*log2e*s over both halves
         float l_run = 0.f;        // running sum of exp2(.) over this half's columns
         bool ok = true;
@@ -239,7 +239,8 @@ fmha_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
             const bool need_mask = (p.causal && i * FA_BN + FA_BN - 1 > q0) || (i * FA_BN + FA_BN > p.S);
             const int col_limit = p.causal ? min(p.S - 1, q) : p.S - 1;  // last visible key
 
-            // this half's scores, scaled, kept in registers
+            // this half's raw scores, kept in registers (the scale is applied inside the exponent's
+            // FMA; it is positive, so the maximum can be taken on the raw scores)
             float x[HC];
 #pragma unroll
             for (int c = 0; c < HC / 32; ++c) {
@@ -247,14 +248,17 @@ fmha_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
                 tmem_ld_32x32b_x32(s_addr + half * HC + c * 32, v);
                 tmem_wait_ld();
 #pragma unroll
-                for (int j = 0; j < 32; ++j) x[c * 32 + j] = __uint_as_float(v[j]) * sl2;
+                for (int j = 0; j < 32; ++j) x[c * 32 + j] = __uint_as_float(v[j]);
+            }
+            if (need_mask) {
+#pragma unroll
+                for (int j = 0; j < HC; ++j)
+                    if (kv0 + j > col_limit) x[j] = -INFINITY;
             }
             float mx = -INFINITY;
 #pragma unroll
-            for (int j = 0; j < HC; ++j) {
-                if (need_mask && kv0 + j > col_limit) x[j] = -INFINITY;
-                mx = fmaxf(mx, x[j]);
-            }
+            for (int j = 0; j < HC; ++j) mx = fmaxf(mx, x[j]);
+            mx *= sl2;
             // exchange the row maximum with the other half
             asm volatile("st.shared.f32 [%0], %1;" ::"r"(xchg + (half * FA_BM + row) * 4), "f"(mx) : "memory");
             named_barrier_sync(1, 256);
@@ -270,8 +274,8 @@ fmha_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
             uint32_t pk[HC / 2];
 #pragma unroll
             for (int j = 0; j < HC / 2; ++j) {
-                const float e0 = fast_exp2(x[2 * j] - m_safe);
-                const float e1 = fast_exp2(x[2 * j + 1] - m_safe);
+                const float e0 = fast_exp2(fmaf(x[2 * j], sl2, -m_safe));
+                const float e1 = fast_exp2(fmaf(x[2 * j + 1], sl2, -m_safe));
                 sum += e0 + e1;
                 pk[j] = pack_half2(e0, e1);
             }
