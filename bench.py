@@ -29,7 +29,7 @@ if str(ROOT) not in sys.path:
 
 GEMM_N = 8192
 # DRAM bytes (read + write) per 8192^3 launch of the dominant kernel, from one ncu capture
-# (profiles/gemm_f16f32_pair_8192.md: 1.08 GB read + 0.25 GB written).
+# of the CTA-pair kernel (1.08 GB read + 0.25 GB written; summary kept under profiles/).
 NCU_TRAFFIC_BYTES = {"gemm_8192": 1.33e9}
 
 
