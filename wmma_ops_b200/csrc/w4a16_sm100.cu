@@ -296,15 +296,25 @@ w4a16_gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_const
                 else tmem_ld_32x32b_x16(t_addr + c * CH, v);
                 tmem_wait_ld();
                 if constexpr (WM) {
-                    // add the other workers' accumulators in worker order
+                    // add the other workers' accumulators in worker order; the loads of two
+                    // accumulators are in flight together
 #pragma unroll 1
-                    for (int a = 1; a < Cfg::ACCS; ++a) {
-                        uint32_t u[CH];
-                        if constexpr (CH == 32) tmem_ld_32x32b_x32(t_addr + a * BT + c * CH, u);
-                        else tmem_ld_32x32b_x16(t_addr + a * BT + c * CH, u);
+                    for (int a = 1; a < Cfg::ACCS; a += 2) {
+                        uint32_t u0[CH], u1[CH];
+                        if constexpr (CH == 32) {
+                            tmem_ld_32x32b_x32(t_addr + a * BT + c * CH, u0);
+                            if (a + 1 < Cfg::ACCS) tmem_ld_32x32b_x32(t_addr + (a + 1) * BT + c * CH, u1);
+                        } else {
+                            tmem_ld_32x32b_x16(t_addr + a * BT + c * CH, u0);
+                            if (a + 1 < Cfg::ACCS) tmem_ld_32x32b_x16(t_addr + (a + 1) * BT + c * CH, u1);
+                        }
                         tmem_wait_ld();
 #pragma unroll
-                        for (int j = 0; j < CH; ++j) v[j] = __float_as_uint(__uint_as_float(v[j]) + __uint_as_float(u[j]));
+                        for (int j = 0; j < CH; ++j) {
+                            float t = __uint_as_float(v[j]) + __uint_as_float(u0[j]);
+                            if (a + 1 < Cfg::ACCS) t += __uint_as_float(u1[j]);
+                            v[j] = __float_as_uint(t);
+                        }
                     }
                 }
                 if (part != nullptr) {
@@ -362,9 +372,11 @@ w4a16_gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_const
 
             if (nsl > 1) {
                 // the last slice of this tile to finish sums all partials in slice order
-                __threadfence();
+                // One release for the whole CTA: the barrier orders the 128 threads' partial stores
+                // before thread 0's gpu-scope fence, which is cumulative over them.
                 named_barrier_sync(1, 128);
                 if (et == 0) {
+                    __threadfence();
                     const int old = atomicAdd(p.counters + tile_id, 1);
                     const uint32_t last = (old == nsl - 1) ? 1u : 0u;
                     if (last) p.counters[tile_id] = 0;  // ready for the next call
