@@ -305,6 +305,41 @@ def measure_layer(w, dev, rank, world, steps):
             "variants": out}
 
 
+def cpu_side_baselines():
+    """The reference's CPU path for the other workloads (fp32 torch on the host cores), each on a
+    bounded sample of a few seconds: dequantise-then-matmul, softmax attention, the layer."""
+    from oracle import attention as oa
+    from oracle import int4
+    from oracle import layer as olayer
+    threads = torch.get_num_threads()
+    out = {}
+    K, N = 4096, 11008
+    codes, scales = int4.seeded_w4(K, N, 128, seed=7)
+    g = torch.Generator().manual_seed(8)
+    for M in (16, 512):
+        A = torch.randn(M, K, generator=g).half()
+        t0 = time.perf_counter()
+        int4.w4a16_ref(A, codes, scales, 128)
+        dt = time.perf_counter() - t0
+        out[f"w4a16_M{M}"] = {"ms": dt * 1e3, "tflops": 2.0 * M * N * K / dt / 1e12,
+                              "gbs": int4.w4a16_bytes(M, N, K, 128) / dt / 1e9, "cores": threads, "kind": "port",
+                              "sample": f"full product at M={M}: dequantise 4096x11008 to fp16, then fp32 matmul"}
+    Q, Kt, V = oa.seeded_qkv(1, 2, 2048, 128, seed=9)
+    t0 = time.perf_counter()
+    oa.attention_ref(Q, Kt, V, False)
+    dt = time.perf_counter() - t0
+    out["fmha_S2048"] = {"ms": dt * 1e3, "tflops": oa.fmha_flops(1, 2, 2048, 128, False) / dt / 1e12, "cores": threads,
+                         "kind": "port", "sample": "2 of the 128 (batch, head) pairs at S=2048, non-causal"}
+    weights = olayer.make_layer_weights(seed=21)
+    x = torch.randn(256, 4096, generator=g).half()
+    t0 = time.perf_counter()
+    olayer.layer_ref(x, weights)
+    dt = time.perf_counter() - t0
+    out["layer"] = {"ms": dt * 1e3, "tflops": olayer.layer_flops(256) / dt / 1e12, "cores": threads, "kind": "port",
+                    "sample": "256 of the 8192 tokens through the four dequantised linears"}
+    return out
+
+
 def extra_measurements(args, w, dev, rank, world, peaks):
     out = {}
     if world == 1:
@@ -312,6 +347,8 @@ def extra_measurements(args, w, dev, rank, world, peaks):
         out["fmha"] = measure_fmha(w, dev, peaks, world)
         torch.cuda.empty_cache()
     out["layer"] = measure_layer(w, dev, rank, world, args.steps)
+    if world == 1 and rank == 0:
+        out["cpu_other_workloads"] = cpu_side_baselines()
     return out
 
 

@@ -62,6 +62,33 @@ def test_reference_seeded_shapes(cuda, shape):
         assert og.reference_pass(out, ref), name
 
 
+@pytest.mark.parametrize("shape", [(512, 512, 64), (2048, 2048, 128), (4096, 4096, 2048)])
+def test_reference_correctness_script_shapes(cuda, shape):
+    # test_rocwmma_patch.py:50-128: compared with torch's own fp16 matmul on the GPU,
+    # pass if max-rel < 1e-3 or max-abs < 0.1 (0.5 for the large case)
+    M, N, K = shape
+    g = torch.Generator(device="cuda").manual_seed(9)
+    A = torch.randn(M, K, generator=g, device=cuda).half()
+    B = torch.randn(K, N, generator=g, device=cuda).half()
+    C = w.matmul(A, B)
+    ref = torch.matmul(A, B).float()
+    _sync_ok()
+    err = (C - ref).abs().max().item()
+    assert err / ref.abs().max().item() < 1e-3 or err < (0.5 if K >= 2048 else 0.1)
+
+
+def test_cross_kernel_agreement(cuda):
+    # test_fragment_loading.py:175-222: matmul and matmul_asmOpt on 2048x2048x512
+    A, B = og.seeded_ab(2048, 2048, 512, seed=10)
+    a = w.matmul(A.to(cuda), B.to(cuda))
+    b = w.matmul_asmOpt(A.to(cuda), B.to(cuda))
+    c = w.matmul_tiled(A.to(cuda), B.to(cuda), 0)
+    _sync_ok()
+    ref = og.gemm_ref(A, B)
+    assert og.rel_frobenius(a, ref) < TOL and og.rel_frobenius(b, ref) < TOL and og.rel_frobenius(c, ref) < TOL
+    assert (a - c).abs().max().item() < 1e-2
+
+
 def test_config1_512_cubed_alpha_beta_inplace(cuda):
     M = N = K = 512
     A, B = og.seeded_ab(M, N, K, seed=1)

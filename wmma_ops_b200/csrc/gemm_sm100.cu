@@ -276,10 +276,12 @@ gemm_f16f32_kernel(const __grid_constant__ CUtensorMap tmap_a,
 // the leader's barrier); the leader's MMA thread commits to empty[] and acc_full[] of both CTAs
 // (one commit per CTA); both CTAs' epilogue threads arrive on the leader's acc_empty[] (256).
 constexpr int PAIR_BN = 256;
-constexpr int PAIR_STAGES = 6;
-constexpr int PAIR_A_BYTES = BM * BK * 2;            // 16 KB: this CTA's 128 rows
-constexpr int PAIR_B_BYTES = 2 * BK * 64 * 2;        // 16 KB: this CTA's 128 columns (two boxes)
-constexpr int PAIR_STAGE_BYTES = PAIR_A_BYTES + PAIR_B_BYTES;
+constexpr int PAIR_KH = 2;                           // 64-deep k-blocks per pipeline stage
+constexpr int PAIR_STAGES = 6 / PAIR_KH;
+constexpr int PAIR_A_BYTES = BM * BK * 2;            // 16 KB: this CTA's 128 rows of one k-block
+constexpr int PAIR_B_BYTES = 2 * BK * 64 * 2;        // 16 KB: this CTA's 128 columns (two boxes) of one k-block
+constexpr int PAIR_KB_BYTES = PAIR_A_BYTES + PAIR_B_BYTES;
+constexpr int PAIR_STAGE_BYTES = PAIR_KH * PAIR_KB_BYTES;
 constexpr int PAIR_SMEM_BYTES = PAIR_STAGES * PAIR_STAGE_BYTES + 1024 + 256;
 
 __device__ __forceinline__ void decode_pair_unit(const GemmParams& p, int unit, int& mb2, int& nb) {
@@ -349,19 +351,23 @@ gemm_f16f32_pair_kernel(const __grid_constant__ CUtensorMap tmap_a,
                 decode_pair_unit(p, unit, mb2, nb);
                 const int row0 = mb2 * 256 + static_cast<int>(cta_rank) * 128;
                 const int col0 = nb * PAIR_BN + static_cast<int>(cta_rank) * 128;
-                for (int kb = 0; kb < p.kb_total; ++kb) {
+                for (int kb = 0; kb < p.kb_total; kb += PAIR_KH) {
                     if (!mbar_wait(empty_bar(stage), phase ^ 1u)) {
                         report_timeout(p.status, 10, kb);
                         ok = false;
                         break;
                     }
-                    const uint32_t a_dst = smem_base + stage * PAIR_STAGE_BYTES;
-                    const uint32_t b_dst = a_dst + PAIR_A_BYTES;
                     if (cta_rank == 0) mbar_arrive_expect_tx(full_bar(stage), 2 * PAIR_STAGE_BYTES);
                     const uint32_t leader_full = mapa(full_bar(stage), 0);
-                    tma_load_2d_pair(a_dst, &tmap_a, leader_full, kb * BK, row0);
-                    tma_load_2d_pair(b_dst, &tmap_b, leader_full, col0, kb * BK);
-                    tma_load_2d_pair(b_dst + BK * 64 * 2, &tmap_b, leader_full, col0 + 64, kb * BK);
+#pragma unroll
+                    for (int h = 0; h < PAIR_KH; ++h) {
+                        // a k-block past the end of K is filled with zeros by TMA
+                        const uint32_t a_dst = smem_base + stage * PAIR_STAGE_BYTES + h * PAIR_KB_BYTES;
+                        const uint32_t b_dst = a_dst + PAIR_A_BYTES;
+                        tma_load_2d_pair(a_dst, &tmap_a, leader_full, (kb + h) * BK, row0);
+                        tma_load_2d_pair(b_dst, &tmap_b, leader_full, col0, (kb + h) * BK);
+                        tma_load_2d_pair(b_dst + BK * 64 * 2, &tmap_b, leader_full, col0 + 64, (kb + h) * BK);
+                    }
                     if (++stage == PAIR_STAGES) {
                         stage = 0;
                         phase ^= 1u;
@@ -384,20 +390,23 @@ gemm_f16f32_pair_kernel(const __grid_constant__ CUtensorMap tmap_a,
                 }
                 tc_fence_after_sync();
                 const uint32_t d_tmem = tmem_base + acc * PAIR_BN;
-                for (int kb = 0; kb < p.kb_total; ++kb) {
+                for (int kb = 0; kb < p.kb_total; kb += PAIR_KH) {
                     if (!mbar_wait(full_bar(stage), phase)) {
                         report_timeout(p.status, 11, kb);
                         ok = false;
                         break;
                     }
                     tc_fence_after_sync();
-                    const uint32_t a_src = smem_base + stage * PAIR_STAGE_BYTES;
-                    const uint32_t b_src = a_src + PAIR_A_BYTES;
 #pragma unroll
-                    for (int kk = 0; kk < BK / 16; ++kk) {
-                        const uint64_t a_desc = make_smem_desc_sw128(a_src + kk * 32, 16, 1024);
-                        const uint64_t b_desc = make_smem_desc_sw128(b_src + kk * 2048, BK * 64 * 2, 1024);
-                        umma_f16_pair(d_tmem, a_desc, b_desc, idesc, (kb > 0 || kk > 0) ? 1u : 0u);
+                    for (int h = 0; h < PAIR_KH; ++h) {
+                        const uint32_t a_src = smem_base + stage * PAIR_STAGE_BYTES + h * PAIR_KB_BYTES;
+                        const uint32_t b_src = a_src + PAIR_A_BYTES;
+#pragma unroll
+                        for (int kk = 0; kk < BK / 16; ++kk) {
+                            const uint64_t a_desc = make_smem_desc_sw128(a_src + kk * 32, 16, 1024);
+                            const uint64_t b_desc = make_smem_desc_sw128(b_src + kk * 2048, BK * 64 * 2, 1024);
+                            umma_f16_pair(d_tmem, a_desc, b_desc, idesc, (kb > 0 || h > 0 || kk > 0) ? 1u : 0u);
+                        }
                     }
                     umma_commit_pair(empty_bar(stage));
                     umma_commit_pair(mapa(empty_bar(stage), 1));
