@@ -48,6 +48,11 @@ const char* wmma_ops_last_error(void);
 /* Library version: major * 10000 + minor * 100 + patch. */
 int wmma_ops_version(void);
 
+/* Leaves `sms` SMs (0..64, default 0) unoccupied by this library's persistent kernels, so that
+ * kernels of other libraries launched on other streams (a collective that should overlap a
+ * GEMM) find room to run. Process-wide; no counterpart in the reference (it is single-GPU). */
+int wmma_ops_set_sm_margin(int sms);
+
 /* Tile shape and split-K factor for an M x N x K product on a device with num_sms SMs
  * (num_sms <= 0: 148). Replaces select_optimal_tile (wmma_tile_selection.hpp:30-66) and
  * split_k::compute_config (wmma_xor_swizzle.hpp:293-332). Pure host arithmetic. */

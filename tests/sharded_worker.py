@@ -23,10 +23,11 @@ def main():
     dist.init_process_group("nccl", device_id=dev)
     weights = olayer.make_layer_weights(seed=21)
     g = torch.Generator().manual_seed(5)
-    x = torch.randn(256, 4096, generator=g).to(torch.float16)
+    x = torch.randn(1024, 4096, generator=g).to(torch.float16)
     local = {k: (c.to(dev), s.to(dev)) for k, (c, s) in sharded.shard_layer_weights(weights, rank, world).items()}
     ok = True
-    for rdt, chunks, tol in ((torch.float32, 1, 1e-3), (torch.float16, 1, 3e-3)):
+    w.set_sm_margin(16)
+    for rdt, chunks, tol in ((torch.float32, 1, 1e-3), (torch.float16, 1, 3e-3), (torch.float16, 2, 3e-3)):
         layer = sharded.ShardedDecoderLinears(local, world=world, reduce_dtype=rdt, chunks=chunks)
         attn, mlp = layer(x.to(dev))
         torch.cuda.synchronize()

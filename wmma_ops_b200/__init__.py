@@ -29,6 +29,7 @@ from .ops import (  # noqa: F401
     matmul_xor_optimized,
     matmul_zerocopy,
     select_tile,
+    set_sm_margin,
 )
 
 from .attention import flash_attention  # noqa: F401,E402

@@ -32,6 +32,7 @@ _vp = ctypes.c_void_p
 SIGNATURES = {
     "wmma_ops_last_error": (ctypes.c_char_p, []),
     "wmma_ops_version": (_c_int, []),
+    "wmma_ops_set_sm_margin": (_c_int, [_c_int]),
     "wmma_ops_select_tile": (_c_int, [_c_int, _c_int, _c_int, _c_int, ctypes.POINTER(_c_int), ctypes.POINTER(_c_int)]),
     "wmma_ops_gemm_workspace_bytes": (_c_size_t, [_c_int, _c_int, _c_int, _c_int]),
     "wmma_ops_gemm_f16f32": (_c_int, [_vp, _vp, _vp, _vp, _c_int, _c_int, _c_int, _c_float, _c_float,

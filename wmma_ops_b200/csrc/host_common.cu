@@ -15,6 +15,10 @@ void set_error(const char* fmt, ...) {
     va_end(ap);
 }
 
+int g_sm_margin = 0;
+
+int sm_margin() { return g_sm_margin; }
+
 int sm_count() {
     static int cached[64];
     static std::mutex mu;
@@ -27,7 +31,9 @@ int sm_count() {
             n = 148;
         cached[dev] = n;
     }
-    return cached[dev];
+    // SMs left free for other kernels (collectives) that must run beside the persistent ones
+    const int usable = cached[dev] - g_sm_margin;
+    return usable > 8 ? usable : 8;
 }
 
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*,
@@ -85,3 +91,12 @@ int encode_tmap(CUtensorMap* out, CUtensorMapDataType dtype, int rank, const voi
 extern "C" const char* wmma_ops_last_error(void) { return wb::g_err; }
 
 extern "C" int wmma_ops_version(void) { return 100; }
+
+extern "C" int wmma_ops_set_sm_margin(int sms) {
+    if (sms < 0 || sms > 64) {
+        wb::set_error("sm margin must be in 0..64 (got %d)", sms);
+        return WMMA_OPS_ERR_INVALID;
+    }
+    wb::g_sm_margin = sms;
+    return WMMA_OPS_OK;
+}

@@ -31,8 +31,10 @@ void set_error(const char* fmt, ...);  // stores a thread-local message for wmma
         }                            \
     } while (0)
 
-// Number of SMs of the current device (cached per device index).
+// Number of SMs the persistent kernels may occupy on the current device: the device's SM count
+// (cached per device index) minus the margin set with wmma_ops_set_sm_margin.
 int sm_count();
+extern int g_sm_margin;
 
 // Encodes a tiled tensor map. dims/strides are innermost first; strides[0] is implied
 // (element size) and strides[i>0] are in bytes. Returns 0 or WMMA_OPS_ERR_*.

@@ -134,6 +134,12 @@ def _sm_count(device: torch.device) -> int:
     return n
 
 
+def set_sm_margin(sms: int) -> None:
+    """Leaves `sms` SMs free of this library's persistent kernels (process-wide), so that a
+    collective running on another stream can overlap a GEMM."""
+    _lib.check(_lib.load().wmma_ops_set_sm_margin(int(sms)))
+
+
 def select_tile(M: int, N: int, K: int, num_sms: int = 148) -> Tuple[int, int]:
     """(tile_cfg, split_k) for an MxNxK product: the Blackwell counterpart of the reference's
     select_optimal_tile (wmma_tile_selection.hpp:30-66) and split_k::compute_config

@@ -162,6 +162,8 @@ class ShardedDecoderLinears:
         """Same arithmetic with the glue inside the GEMM epilogues: QKV writes half(GLUE_SCALE * acc),
         gate/up writes half(GLUE_SCALE * silu(gate) * up); only the slice copy and the scaling of the
         all-reduced attention output remain as separate (small) kernels."""
+        if self.world > 1 and self.chunks > 1 and x.shape[0] >= 512 * self.chunks:
+            return self._forward_pipelined(x)
         out_dt = self.reduce_dtype
         qkv16 = self._w4(x, "qkv", out_dtype=torch.float16, alpha=GLUE_SCALE)
         o_in = qkv16[:, :self.q_cols].contiguous()
@@ -170,6 +172,56 @@ class ShardedDecoderLinears:
         h = (attn_out * GLUE_SCALE).to(torch.float16)
         act = self._w4(h, "gate_up", epilogue="silu_mul", alpha=GLUE_SCALE)
         mlp_out = self._row_parallel(act, "down")
+        return attn_out, mlp_out
+
+    def _forward_pipelined(self, x: torch.Tensor) -> Tuple[torch.Tensor, torch.Tensor]:
+        """The fused forward on token chunks, alternating between two side streams: while one
+        chunk's partial outputs are being all-reduced (NCCL runs on its own stream), the other
+        chunk's GEMMs run. The GEMM kernels are persistent and would fill every SM, so the caller
+        should leave a few SMs free for the collective (wmma_ops_b200.set_sm_margin)."""
+        import torch.distributed as dist
+        out_dt = self.reduce_dtype
+        T = x.shape[0]
+        n = self.chunks
+        bounds = [(i * T // n, (i + 1) * T // n) for i in range(n)]
+        main = torch.cuda.current_stream(x.device)
+        if getattr(self, "_streams", None) is None:
+            self._streams = [torch.cuda.Stream(device=x.device) for _ in range(2)]
+        attn_out = torch.empty((T, self.packed["o"][1].shape[1]), dtype=out_dt, device=x.device)
+        mlp_out = torch.empty_like(attn_out)
+        for st in self._streams:
+            st.wait_stream(main)
+        keep, stage1, stage2 = [], [], []
+        for c, (a, b) in enumerate(bounds):
+            with torch.cuda.stream(self._streams[c % 2]):
+                qkv16 = self._w4(x[a:b], "qkv", out_dtype=torch.float16, alpha=GLUE_SCALE)
+                o_in = qkv16[:, :self.q_cols].contiguous()
+                part = self._w4(o_in, "o", out_dtype=out_dt)
+                work = dist.all_reduce(part, op=dist.ReduceOp.SUM, async_op=True)
+                stage1.append((part, work))
+                keep += [qkv16, o_in]
+        for c, (a, b) in enumerate(bounds):
+            with torch.cuda.stream(self._streams[c % 2]):
+                part, work = stage1[c]
+                work.wait()
+                attn_out[a:b].copy_(part)
+                h = (part * GLUE_SCALE).to(torch.float16)
+                act = self._w4(h, "gate_up", epilogue="silu_mul", alpha=GLUE_SCALE)
+                part2 = self._w4(act, "down", out_dtype=out_dt)
+                work2 = dist.all_reduce(part2, op=dist.ReduceOp.SUM, async_op=True)
+                stage2.append((part2, work2))
+                keep += [h, act]
+        for c, (a, b) in enumerate(bounds):
+            with torch.cuda.stream(self._streams[c % 2]):
+                part2, work2 = stage2[c]
+                work2.wait()
+                mlp_out[a:b].copy_(part2)
+        for st in self._streams:
+            main.wait_stream(st)
+        # the intermediates were allocated on the side streams: tell the allocator the main stream
+        # (which now depends on them) may still be using them
+        for t in keep + [p for p, _ in stage1] + [p for p, _ in stage2]:
+            t.record_stream(main)
         return attn_out, mlp_out
 
     __call__ = forward
