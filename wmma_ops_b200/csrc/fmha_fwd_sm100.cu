@@ -7,7 +7,8 @@
 // One CTA owns 128 query rows of one (batch, head) and walks the key/value sequence in tiles
 // of 64 with an online softmax; two such CTAs share an SM:
 //   warp 0      TMA producer: Q once, then K and V tiles into two-stage rings
-//   warp 1      TMEM owner and MMA issuer: S = Q K^T (fp32, TMEM), O += P V (fp32, TMEM)
+//   warp 1      TMEM owner and issuer of S = Q K^T (fp32, TMEM)
+//   warp 10     issuer of O += P V (fp32, TMEM)
 //   warps 2..9  softmax: two warps per TMEM lane quadrant, each thread one query row and half of
 //               the tile's keys; read S from TMEM, keep the running max and sum, write P (fp16)
 //               back into tensor memory over S, from where P V reads it as its A operand,
@@ -21,7 +22,7 @@
 namespace wb {
 
 constexpr int FA_BM = 128;  // query rows per CTA
-constexpr int FA_THREADS = 320;  // warp 0 producer, warp 1 MMA, warps 2..9 softmax
+constexpr int FA_THREADS = 352;  // warp 0 producer, warp 1 Q.K^T issuer, warps 2..9 softmax, warp 10 P.V issuer
 
 // BN = keys per tile. BN = 64 keeps a CTA at 96 KB of shared memory and 256 TMEM columns (D = 128),
 // so two CTAs share an SM and one CTA's softmax latency hides behind the other's work.
@@ -59,6 +60,13 @@ __device__ __forceinline__ float fast_exp2(float x) {
     float y;
     asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
     return y;
+}
+
+// three-input maximum (one instruction on sm_100)
+__device__ __forceinline__ float fmax3(float a, float b, float c) {
+    float d;
+    asm("max.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c));
+    return d;
 }
 
 __device__ __forceinline__ uint32_t pack_half2(float a, float b) {
@@ -109,7 +117,7 @@ fmha_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
             mbar_init(v_full(s), 1);
             mbar_init(v_empty(s), 1);
             mbar_init(s_full(s), 1);
-            mbar_init(s_empty(s), 1);  // unused: S buffers are recycled in MMA issue order
+            mbar_init(s_empty(s), 1);
             mbar_init(p_ready(s), 256);
         }
         mbar_init(pv_done, 1);
@@ -158,37 +166,19 @@ fmha_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
             }
         }
     } else if (warp == 1) {
-        // ------------------------------------------------------------ MMA issuer
+        // ------------------------------------------------------------ S = Q K^T issuer
+        // Two issuing threads (this one and warp 10 for P V): a single thread pays 40-75 ns per
+        // tcgen05.mma / commit / wait, about 20 of them per 64-key tile, which was longer than
+        // the tile's tensor time.
         if (lane == 0) {
             constexpr uint32_t idesc_s = make_idesc_f16_f32(FA_BM, FA_BN, false, false);
-            constexpr uint32_t idesc_o = make_idesc_f16_f32(FA_BM, D, false, true);
             bool ok = mbar_wait(q_full, 0);
             if (!ok) fa_report(p.status, 1, -1);
-            auto issue_pv = [&](int i) -> bool {
-                const int s = i & 1;
-                const uint32_t ph = (i >> 1) & 1;
-                if (!mbar_wait(v_full(s), ph) || !mbar_wait(p_ready(s), ph)) {
-                    fa_report(p.status, 1, 1000 + i);
-                    return false;
-                }
-                tc_fence_after_sync();
-#pragma unroll
-                for (int kk = 0; kk < FA_BN / 16; ++kk) {
-                    // P (fp16, written by the softmax warps over the first 64 columns of S buffer s) is
-                    // the A operand straight from tensor memory: 16 keys = 8 columns per MMA.
-                    // V: MN-major, 16 keys = 2048 bytes further; 64-wide d blocks KV_BOX_BYTES apart
-                    const uint64_t b_desc = make_smem_desc_sw128(v_smem(s) + kk * 2048, Cfg::KV_BOX_BYTES, 1024);
-                    umma_f16_ts(tmem_base + Cfg::O_COL, tmem_base + (s ? Cfg::S_COL1 : Cfg::S_COL0) + kk * 8, b_desc,
-                                idesc_o, (i > 0 || kk > 0) ? 1u : 0u);
-                }
-                umma_commit(v_empty(s));
-                umma_commit(pv_done);
-                return true;
-            };
             for (int i = 0; ok && i < n_tiles; ++i) {
                 const int s = i & 1;
                 const uint32_t ph = (i >> 1) & 1;
-                if (!mbar_wait(k_full(s), ph)) {
+                // S buffer s is free once P V of tile i-2 (which read P from it) has completed
+                if (!mbar_wait(k_full(s), ph) || !mbar_wait(s_empty(s), ph ^ 1u)) {
                     fa_report(p.status, 1, i);
                     ok = false;
                     break;
@@ -205,9 +195,33 @@ fmha_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
                 }
                 umma_commit(k_empty(s));
                 umma_commit(s_full(s));
-                if (i > 0) ok = issue_pv(i - 1);
             }
-            if (ok && n_tiles > 0) issue_pv(n_tiles - 1);
+        }
+    } else if (warp == 10) {
+        // ------------------------------------------------------------ O += P V issuer
+        if (lane == 0) {
+            constexpr uint32_t idesc_o = make_idesc_f16_f32(FA_BM, D, false, true);
+            for (int i = 0; i < n_tiles; ++i) {
+                const int s = i & 1;
+                const uint32_t ph = (i >> 1) & 1;
+                if (!mbar_wait(v_full(s), ph) || !mbar_wait(p_ready(s), ph)) {
+                    fa_report(p.status, 3, i);
+                    break;
+                }
+                tc_fence_after_sync();
+#pragma unroll
+                for (int kk = 0; kk < FA_BN / 16; ++kk) {
+                    // P (fp16, written by the softmax warps over the start of S buffer s) is the A
+                    // operand straight from tensor memory: 16 keys = 8 columns per MMA.
+                    // V: MN-major, 16 keys = 2048 bytes further; 64-wide d blocks KV_BOX_BYTES apart
+                    const uint64_t b_desc = make_smem_desc_sw128(v_smem(s) + kk * 2048, Cfg::KV_BOX_BYTES, 1024);
+                    umma_f16_ts(tmem_base + Cfg::O_COL, tmem_base + (s ? Cfg::S_COL1 : Cfg::S_COL0) + kk * 8, b_desc,
+                                idesc_o, (i > 0 || kk > 0) ? 1u : 0u);
+                }
+                umma_commit(v_empty(s));
+                umma_commit(s_empty(s));
+                umma_commit(pv_done);
+            }
         }
     } else {
         // ------------------------------------------------------------ softmax warps (2..9)
@@ -255,10 +269,13 @@ fmha_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
                 for (int j = 0; j < HC; ++j)
                     if (kv0 + j > col_limit) x[j] = -INFINITY;
             }
-            float mx = -INFINITY;
+            float mx0 = -INFINITY, mx1 = -INFINITY;   // two chains of three-input maxima
 #pragma unroll
-            for (int j = 0; j < HC; ++j) mx = fmaxf(mx, x[j]);
-            mx *= sl2;
+            for (int j = 0; j < HC; j += 4) {
+                mx0 = fmax3(mx0, x[j], x[j + 1]);
+                mx1 = fmax3(mx1, x[j + 2], x[j + 3]);
+            }
+            float mx = fmaxf(mx0, mx1) * sl2;
             // exchange the row maximum with the other half
             asm volatile("st.shared.f32 [%0], %1;" ::"r"(xchg + (half * FA_BM + row) * 4), "f"(mx) : "memory");
             named_barrier_sync(1, 256);

@@ -224,4 +224,17 @@ class ShardedDecoderLinears:
             t.record_stream(main)
         return attn_out, mlp_out
 
+    def capture(self, x: torch.Tensor):
+        """Captures forward(x) (GEMMs, glue and the NCCL all-reduces) into a CUDA graph and returns
+        (replay, attn_out, mlp_out): calling replay() re-runs the layer on the current contents of
+        `x` and refreshes the two output tensors. At 8 GPUs the per-rank kernels take tens of
+        microseconds, less than the host needs to launch them one by one."""
+        for _ in range(2):     # warm-up outside capture: lazy initialisation, workspaces, NCCL set-up
+            self.forward(x)
+        torch.cuda.synchronize(x.device)
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph):
+            attn_out, mlp_out = self.forward(x)
+        return graph.replay, attn_out, mlp_out
+
     __call__ = forward
