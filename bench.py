@@ -312,6 +312,21 @@ def measure_layer(w, dev, rank, world, steps):
         out[label] = {"ms": ms, "tflops": olayer.layer_flops(tokens) / ms / 1e9, "tokens_per_s": tokens / ms * 1e3}
         del layer
     w.set_sm_margin(0)
+    if world > 1:
+        # partial outputs written into symmetric memory and summed through the NVSwitch by the
+        # library's own multimem kernel instead of NCCL
+        try:
+            from wmma_ops_b200.collective import SwitchAllReduce
+            sw = SwitchAllReduce(tokens, 4096, dev)
+            layer = sharded.ShardedDecoderLinears(local, world=world, reduce_dtype=torch.float16, switch=sw)
+            for _ in range(3):
+                layer(x)
+            ms = time_region(lambda: layer(x), max(3, min(steps, 10)), world, dev)
+            out["fp16_reduce_nvswitch_multimem"] = {"ms": ms, "tflops": olayer.layer_flops(tokens) / ms / 1e9,
+                                                    "tokens_per_s": tokens / ms * 1e3}
+            del layer
+        except Exception as e:  # no symmetric memory / multicast on this system
+            out["fp16_reduce_nvswitch_multimem"] = {"error": f"{type(e).__name__}: {str(e)[:200]}"}
     best = max((r for r in out.values() if "tflops" in r), key=lambda r: r["tflops"])
     return {"workload": "llama7b_linears_w4a16_8192_tokens", "scaling": "strong", "n_gpus": world,
             "parallelism": f"tp{world}", "ms": best["ms"], "tflops": best["tflops"], "tokens_per_s": best["tokens_per_s"],

@@ -117,17 +117,25 @@ int wmma_ops_int4_unpack(const void* qweight, void* codes_u8, int K, int N, void
 int wmma_ops_int4_dequant(const void* qweight, const void* scales, void* W_f16, int K, int N,
                           int group_size, void* stream);
 
-/* Bytes of scratch wmma_ops_w4a16_gemm needs (split-K partials + arrival counters). */
+/* Bytes of scratch wmma_ops_w4a16_gemm needs for this shape and split_k (partial sums + arrival
+ * counters); 0 when the plan has no partial sums. The buffer must be zero-filled once: the kernels
+ * leave the counters (its first 64 KB) at zero, so one buffer can serve calls of any shape. */
 size_t wmma_ops_w4a16_workspace_bytes(int M, int N, int K, int split_k);
 
-/* Split-K factor wmma_ops_w4a16_gemm picks when split_k == 0. */
+/* Split-K factor wmma_ops_w4a16_gemm picks when split_k == 0 and M > 16. */
 int wmma_ops_w4a16_select_split(int M, int N, int K, int num_sms);
 
 /* C[M,N] fp32 = A[M,K] fp16 . W, W dequantised on the fly from qweight / scales inside the
- * kernel (shared memory), never materialised in global memory.
+ * kernel, never materialised in global memory.
  * Requirements: K % 64 == 0, K % group_size == 0, group_size % 64 == 0, N % 8 == 0.
- * split_k: 0 = auto, 1 = none, > 1 needs workspace (zeroed counters are maintained by the
- * kernel itself after the first call; pass a buffer that was zero-filled once). */
+ * split_k: 0 = the library's plan, 1 = none, > 1 = that many K slices (needs workspace).
+ * With split_k == 0 and M <= 16 (decode) the product runs on the streaming kernel: every SM
+ * streams an equal share of the packed weights, column tiles shared by several CTAs are summed in
+ * CTA order by the last CTA to finish (deterministic), and it always needs the workspace. That
+ * kernel multiplies by the exact integers code - 8 and applies the fp16 group scale to the fp32
+ * sum of each 64-deep block, so its result differs from "dequantise to fp16, then multiply" by
+ * the fp16 rounding of the weights (about 2e-4 relative); the tcgen05 kernel used otherwise
+ * multiplies by the fp16-rounded weights of wmma_ops_int4_dequant. */
 int wmma_ops_w4a16_gemm(const void* A, const void* qweight, const void* scales, void* C, int M,
                         int N, int K, int group_size, int split_k, void* workspace,
                         size_t workspace_bytes, int* status, void* stream);
@@ -138,13 +146,24 @@ int wmma_ops_w4a16_gemm(const void* A, const void* qweight, const void* scales, 
  *   WMMA_OPS_W4_OUT_F16_SILU_MUL  C fp16 [M,N/2] = half(alpha * silu(gate) * up), where in every
  *                                 128-column tile of the weight the first 64 columns are gate columns
  *                                 and the last 64 the up columns of the same 64 outputs (N % 128 == 0).
- * The fp16 modes need a plan without partial sums: pass split_k = 1. */
+ * With M > 16 the fp16 modes run without partial sums (split_k 0 or 1). */
 #define WMMA_OPS_W4_OUT_F32 0
 #define WMMA_OPS_W4_OUT_F16 1
 #define WMMA_OPS_W4_OUT_F16_SILU_MUL 2
 int wmma_ops_w4a16_gemm_ex(const void* A, const void* qweight, const void* scales, void* C, int M, int N,
                            int K, int group_size, int split_k, int out_mode, float alpha, void* workspace,
                            size_t workspace_bytes, int* status, void* stream);
+
+/* Sum of an fp16 buffer over the ranks of one NVSwitch domain, in place, for the row-parallel
+ * outputs of the sharded layer (no counterpart in the reference, which is single-GPU).
+ * multicast_ptr is the NVLink multicast address of a buffer of n_halves fp16 values that every
+ * rank holds in symmetric memory (torch.distributed._symmetric_memory gives both). The caller
+ * makes sure, with a barrier across the ranks on `stream`, that every rank's values are written
+ * before any rank calls this, and that every rank's call has finished before the sums are read.
+ * Rank `rank` reduces the rank-th of `world` slices through the switch (multimem.ld_reduce, fp32
+ * accumulation) and stores the result to all ranks (multimem.st). max_ctas <= 0: all SMs. */
+int wmma_ops_multimem_allreduce_f16(void* multicast_ptr, size_t n_halves, int rank, int world, int max_ctas,
+                                    void* stream);
 
 /* Flash-attention forward: O = softmax(scale * Q K^T [+ causal mask]) V per (b,h).
  * Q, K, V, O are [B,H,S,D] fp16 contiguous; the signature documented in the reference's

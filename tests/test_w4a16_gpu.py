@@ -185,3 +185,56 @@ def test_w4a16_errors(cuda):
         w.matmul_w4a16(A, q, sc, 128, epilogue="gelu")
     with pytest.raises(RuntimeError, match="alpha is only applied"):
         w.matmul_w4a16(A, q, sc, 128, alpha=2.0)
+
+
+# ---- streaming decode kernel (M <= 16, library-chosen plan) --------------------------------------
+# It applies the fp16 group scale to the fp32 sum of a 64-deep block instead of rounding every
+# weight * scale product to fp16 first, so it sits about 2e-4 (relative Frobenius) from the oracle,
+# which dequantises to fp16: inside the 1e-3 bound, but not the 1e-6 of the tcgen05 path.
+
+@pytest.mark.parametrize("case", [
+    (1, 128, 64, 64), (2, 8, 64, 64), (5, 136, 512, 64), (9, 1000, 2048, 128), (16, 256, 512, 128),
+    (8, 384, 192, 192), (7, 4096, 11008, 128), (16, 40000, 64, 64), (3, 4096, 4096, 64), (12, 11008, 4096, 128),
+])
+def test_streaming_decode_shapes(cuda, case):
+    M, N, K, group = case
+    assert _w4_case(cuda, M, N, K, group, 0, seed=21) < TOL
+
+
+@pytest.mark.parametrize("M", [1, 8, 9, 16])
+def test_streaming_decode_output_modes(cuda, M):
+    K, F = 1024, 640
+    codes, scales = int4.seeded_w4(K, 2 * F, 128, seed=23)
+    A, _ = og.seeded_ab(M, 8, K, seed=24)
+    ref = int4.w4a16_ref(A, codes, scales, 128)
+    q, sc = w.int4_prepack(codes.to(cuda), scales.to(cuda), 128)
+    out16 = w.matmul_w4a16(A.to(cuda), q, sc, 128, out_dtype=torch.float16, alpha=0.5)
+    ci, si = w.interleave_gate_up(codes.to(cuda), scales.to(cuda))
+    qi, sci = w.int4_prepack(ci, si, 128)
+    act = w.matmul_w4a16(A.to(cuda), qi, sci, 128, epilogue="silu_mul", alpha=0.25)
+    _sync_ok()
+    assert out16.dtype == torch.float16 and tuple(out16.shape) == (M, 2 * F)
+    assert og.rel_frobenius(out16.float(), 0.5 * ref) < TOL
+    assert act.dtype == torch.float16 and tuple(act.shape) == (M, F)
+    assert og.rel_frobenius(act.float(), 0.25 * torch.nn.functional.silu(ref[:, :F]) * ref[:, F:]) < 2e-3
+
+
+def test_streaming_decode_reuses_one_workspace_across_shapes(cuda):
+    # products with few and with many column tiles share the library's workspace: the arrival
+    # counters sit in a fixed area, so one call's partial sums never land in the next call's counters
+    shapes = [(4, 256, 4096), (16, 11008, 4096), (2, 128, 8192), (16, 11008, 4096), (4, 256, 4096)]
+    data = {}
+    for (M, N, K) in set(shapes):
+        codes, scales = int4.seeded_w4(K, N, 128, seed=31)
+        A, _ = og.seeded_ab(M, 8, K, seed=32)
+        q, sc = w.int4_prepack(codes.to(cuda), scales.to(cuda), 128)
+        data[(M, N, K)] = (A.to(cuda), q, sc, int4.w4a16_ref(A, codes, scales, 128))
+    outs = {}
+    for shape in shapes:
+        A, q, sc, ref = data[shape]
+        C = w.matmul_w4a16(A, q, sc, 128)
+        _sync_ok()
+        assert og.rel_frobenius(C, ref) < TOL
+        if shape in outs:
+            assert torch.equal(C, outs[shape])      # deterministic across calls
+        outs[shape] = C

@@ -51,6 +51,7 @@ SIGNATURES = {
                                         _vp, _c_size_t, _vp, _vp]),
     "wmma_ops_fmha_fwd": (_c_int, [_vp, _vp, _vp, _vp, _c_int, _c_int, _c_int, _c_int, _c_float, _c_int,
                                    _vp, _vp]),
+    "wmma_ops_multimem_allreduce_f16": (_c_int, [_vp, _c_size_t, _c_int, _c_int, _c_int, _vp]),
 }
 
 _lib = None

@@ -22,7 +22,9 @@ SOURCES = [
     "host_common.cu",
     "gemm_sm100.cu",
     "w4a16_sm100.cu",
+    "w4a16_stream_sm100.cu",
     "fmha_fwd_sm100.cu",
+    "allreduce_sm100.cu",
 ]
 
 NVCC_FLAGS = [

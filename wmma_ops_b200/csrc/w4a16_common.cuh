@@ -18,6 +18,7 @@ constexpr int W4_THREADS = 512;
 constexpr int W4_DQ_WARPS = 8;     // each dequant warp expands a whole 4 KB block; 8 blocks in flight
 
 struct W4Params {
+    const __half* X;   // activations [M, K] (read directly by the streaming decode kernel)
     const uint32_t* qweight;
     const __half* scales;
     float* C;          // fp32 output (out_mode 0)
@@ -32,6 +33,7 @@ struct W4Params {
     int max_slices;    // slices a tile can have (= split in the classic plan): stride of partials
     int kb_total;
     int group_kb;      // k-blocks per scale group (group_size / 64)
+    int group_shift;   // log2(group_kb) when it is a power of two, else -1
     int* status;
 };
 
@@ -136,5 +138,28 @@ __device__ __forceinline__ uint32_t dq_pair(uint32_t t, __half2 scale2) {
     return *reinterpret_cast<const uint32_t*>(&r);
 }
 
+// ---------------------------------------------------------------- streaming decode kernel
+// (w4a16_stream_sm100.cu) for products with at most W4_STREAM_MAX_M activation rows.
+constexpr int W4_STREAM_MAX_M = 16;
+
+// Bytes at the start of a workspace that hold the per-tile arrival counters. The area has a fixed
+// size for every product with up to 16384 tiles, so that a caller who reuses one zero-initialised
+// buffer for products of different shapes never gets one call's partial sums into the counters of
+// the next (the kernels leave the counters at zero).
+inline size_t w4_counter_bytes(int tiles) {
+    const size_t need = (static_cast<size_t>(tiles) * 4 + 255) / 256 * 256;
+    return need < 65536 ? 65536 : need;
+}
+
+struct W4StreamPlan {
+    int n_tiles, kb_total, grid, max_slices;
+    size_t workspace_bytes() const {
+        return w4_counter_bytes(n_tiles) + static_cast<size_t>(n_tiles) * max_slices * W4_STREAM_MAX_M * W4_TILE_N * sizeof(float);
+    }
+};
+
+W4StreamPlan w4_stream_plan(int N, int K, int sms);
+// p.n_tiles, p.kb_total, p.max_slices, p.counters and p.partials must follow the plan.
+int w4_stream_launch(const W4Params& p, int grid, cudaStream_t stream);
 
 }  // namespace wb

@@ -492,7 +492,12 @@ static int w4_select_split(int M, int N, int K, int sms) {
     return 1;
 }
 
-static size_t w4_counter_bytes(int tiles) { return (static_cast<size_t>(tiles) * 4 + 255) / 256 * 256; }
+// Products with few activation rows and no explicit K split go to the streaming decode kernel.
+static bool w4_use_stream(int M, int N, int K, int split_k) {
+    const long long blocks = static_cast<long long>((N + W4_TILE_N - 1) / W4_TILE_N) * (K / W4_BK);
+    return M >= 1 && M <= W4_STREAM_MAX_M && split_k == 0 && blocks < (1ll << 30);
+}
+
 
 // How a product is cut into work units.
 struct W4Plan {
@@ -614,6 +619,7 @@ extern "C" int wmma_ops_w4a16_select_split(int M, int N, int K, int num_sms) {
 
 extern "C" size_t wmma_ops_w4a16_workspace_bytes(int M, int N, int K, int split_k) {
     if (M < 1 || N < 8 || K < 64 || K % 64 != 0) return 0;
+    if (wb::w4_use_stream(M, N, K, split_k)) return wb::w4_stream_plan(N, K, wb::sm_count()).workspace_bytes();
     return wb::w4_make_plan(M, N, K, split_k, wb::sm_count()).workspace_bytes();
 }
 
@@ -648,9 +654,12 @@ extern "C" int wmma_ops_w4a16_gemm_ex(const void* A, const void* qweight, const 
                "scales must be 16-byte aligned");
 
     const int sms = sm_count();
+    // fp16 and fused outputs of the tcgen05 kernel come straight from the accumulators
+    if (split_k == 0 && out_mode != WMMA_OPS_W4_OUT_F32 && !w4_use_stream(M, N, K, split_k)) split_k = 1;
     const W4Plan plan = w4_make_plan(M, N, K, split_k, sms);
     const int bt = plan.bt;
     W4Params p;
+    p.X = static_cast<const __half*>(A);
     p.qweight = static_cast<const uint32_t*>(qweight);
     p.scales = static_cast<const __half*>(scales);
     p.C = static_cast<float*>(C);
@@ -664,12 +673,35 @@ extern "C" int wmma_ops_w4a16_gemm_ex(const void* A, const void* qweight, const 
     p.t_tiles = plan.t_tiles;
     p.kb_total = plan.kb_total;
     p.group_kb = group_size / 64;
+    p.group_shift = -1;
+    for (int sh = 0; sh < 24; ++sh)
+        if ((1 << sh) == p.group_kb) p.group_shift = sh;
     p.status = status;
     p.split = plan.split;
     p.balanced = plan.balanced;
     p.max_slices = plan.max_slices;
     p.partials = nullptr;
     p.counters = nullptr;
+    if (w4_use_stream(M, N, K, split_k)) {
+        // decode: one pass over the packed weights, all SMs streaming equal shares
+        const W4StreamPlan sp = w4_stream_plan(N, K, sms);
+        p.n_tiles = sp.n_tiles;
+        p.t_tiles = 1;
+        p.kb_total = sp.kb_total;
+        p.split = 1;
+        p.balanced = 0;
+        p.max_slices = sp.max_slices;
+        const size_t need = sp.workspace_bytes();
+        WB_REQUIRE(workspace != nullptr && workspace_bytes >= need, WMMA_OPS_ERR_WORKSPACE,
+                   "w4a16: a product with M <= %d needs %zu bytes of zero-initialised workspace (got %zu); see "
+                   "wmma_ops_w4a16_workspace_bytes",
+                   W4_STREAM_MAX_M, need, workspace_bytes);
+        WB_REQUIRE(reinterpret_cast<uintptr_t>(workspace) % 16 == 0, WMMA_OPS_ERR_INVALID,
+                   "workspace must be 16-byte aligned");
+        p.counters = static_cast<int*>(workspace);
+        p.partials = reinterpret_cast<float*>(static_cast<uint8_t*>(workspace) + w4_counter_bytes(p.n_tiles));
+        return w4_stream_launch(p, sp.grid, stream);
+    }
     WB_REQUIRE(out_mode == WMMA_OPS_W4_OUT_F32 || !plan.partials(), WMMA_OPS_ERR_INVALID,
                "w4a16: fp16 / fused outputs need a plan without partial sums (pass split_k = 1)");
     if (plan.partials()) {

@@ -7,7 +7,7 @@ with fp16 operands and fp32 accumulation.
 """
 from __future__ import annotations
 
-from typing import Tuple
+from typing import Optional, Tuple
 
 import torch
 
@@ -93,13 +93,15 @@ def interleave_gate_up(codes: torch.Tensor, scales: torch.Tensor) -> Tuple[torch
 
 def matmul_w4a16(A: torch.Tensor, qweight: torch.Tensor, scales: torch.Tensor, group_size: int = 128,
                  split_k: int = 0, out_dtype: torch.dtype = torch.float32, alpha: float = 1.0,
-                 epilogue: str = "none") -> torch.Tensor:
-    """C [M,N] = A fp16 [M,K] @ dequant(qweight, scales); the weights are expanded to fp16 inside the
-    kernel's shared memory. split_k=0 lets the library choose.
+                 epilogue: str = "none", out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """C [M,N] = A fp16 [M,K] @ dequant(qweight, scales); the weights are expanded inside the kernel,
+    never written to memory. split_k=0 lets the library choose: up to 16 rows go to the streaming
+    decode kernel (all SMs stream equal shares of the packed weights), more rows to the tcgen05 kernel.
 
     out_dtype=torch.float32 (default) returns the fp32 accumulators. out_dtype=torch.float16 returns
     half(alpha * acc). epilogue="silu_mul" (weights prepared with interleave_gate_up) returns
-    half(alpha * silu(gate) * up) of shape [M, N/2]."""
+    half(alpha * silu(gate) * up) of shape [M, N/2]. `out`, if given, is the contiguous tensor of that
+    shape and dtype the result is written to (for example a buffer in symmetric memory)."""
     _require(A.is_cuda and qweight.is_cuda and scales.is_cuda, "Inputs must be CUDA tensors")
     _require(A.device == qweight.device and A.device == scales.device, "Inputs must be on same device")
     _require(A.dtype == torch.float16, "Inputs must be float16")
@@ -125,10 +127,12 @@ def matmul_w4a16(A: torch.Tensor, qweight: torch.Tensor, scales: torch.Tensor, g
     else:
         _require(float(alpha) == 1.0, "alpha is only applied to float16 outputs")
         mode, C = OUT_F32, torch.empty((M, N), dtype=torch.float32, device=dev)
+    if out is not None:
+        _require(out.is_cuda and out.device == dev and out.dtype == C.dtype and tuple(out.shape) == tuple(C.shape)
+                 and out.is_contiguous(), "out must be a contiguous CUDA tensor of the result's shape and dtype")
+        C = out
     if M == 0:
         return C
-    if mode != OUT_F32 and split_k == 0:
-        split_k = 1   # fp16 outputs are written straight from the accumulators: no partial sums
     with torch.cuda.device(dev):
         ws_ptr, ws_bytes = None, 0
         need = lib.wmma_ops_w4a16_workspace_bytes(M, N, K, split_k)   # split_k = 0: the library's own plan

@@ -93,8 +93,14 @@ class ShardedDecoderLinears:
 
     def __init__(self, local_weights: Dict[str, Tuple[torch.Tensor, torch.Tensor]], world: int = 1,
                  group: int = GROUP, matmul: Optional[Callable] = None, all_reduce: Optional[Callable] = None,
-                 reduce_dtype: torch.dtype = torch.float32, chunks: int = 1):
+                 reduce_dtype: torch.dtype = torch.float32, chunks: int = 1, switch=None):
         self.world = world
+        # optional collective.SwitchAllReduce: the row-parallel GEMMs then write fp16 partial outputs
+        # into its symmetric buffers and the sum is done through the NVSwitch by the library's own
+        # kernel; forward() then returns views of those buffers (valid until the next forward)
+        self.switch = switch if world > 1 else None
+        if self.switch is not None and reduce_dtype != torch.float16:
+            raise ValueError("the NVSwitch all-reduce sums fp16 buffers: use reduce_dtype=torch.float16")
         self.group = group
         self.reduce_dtype = reduce_dtype
         self.chunks = max(1, chunks)
@@ -167,6 +173,15 @@ class ShardedDecoderLinears:
         out_dt = self.reduce_dtype
         qkv16 = self._w4(x, "qkv", out_dtype=torch.float16, alpha=GLUE_SCALE)
         o_in = qkv16[:, :self.q_cols].contiguous()
+        if self.switch is not None:
+            T = x.shape[0]
+            self._w4(o_in, "o", out_dtype=torch.float16, out=self.switch.buffer(0, T))
+            attn_out = self.switch.reduce(0, T)
+            h = (attn_out * GLUE_SCALE).to(torch.float16)
+            act = self._w4(h, "gate_up", epilogue="silu_mul", alpha=GLUE_SCALE)
+            self._w4(act, "down", out_dtype=torch.float16, out=self.switch.buffer(1, T))
+            mlp_out = self.switch.reduce(1, T)
+            return attn_out, mlp_out
         self._matmul = lambda a, name: self._w4(a, name, out_dtype=out_dt)  # noqa: E731
         attn_out = self._row_parallel(o_in, "o")
         h = (attn_out * GLUE_SCALE).to(torch.float16)
