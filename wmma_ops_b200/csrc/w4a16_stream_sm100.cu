@@ -33,13 +33,21 @@ namespace wb {
 constexpr int SD_KLANES = 8;
 constexpr int SD_WARPS = 2 * SD_KLANES;
 constexpr int SD_THREADS = SD_WARPS * 32;
-constexpr int SD_DEPTH = 4;                  // slots per warp
 constexpr int SD_ITEM_BYTES = W4_RAW_BYTES / 2;  // 64 columns x 64 k
 constexpr int SD_RED_PITCH = 64 + 4;         // floats; rows 2t of a quad of lanes land 8 banks apart
-constexpr int SD_RING_BYTES = SD_WARPS * SD_DEPTH * SD_ITEM_BYTES;
-constexpr int SD_RED_BYTES = SD_WARPS * 16 * SD_RED_PITCH * 4;
-constexpr int SD_SMEM_BYTES = 1024 + SD_RING_BYTES + SD_RED_BYTES + SD_WARPS * SD_DEPTH * 8 + 64;
-static_assert(SD_SMEM_BYTES <= 232448, "streaming decode kernel: shared memory over the per-CTA limit");
+
+// Shared-memory budget. HI (9..16 activation rows) keeps 16-row warp tiles and a shallower ring.
+template <bool HI>
+struct SdCfg {
+    static constexpr int DEPTH = HI ? 2 : 4;                  // ring slots per warp
+    static constexpr int ROWS8 = HI ? 2 : 1;                  // 8-row groups of the MMA tile in use
+    static constexpr int RING_BYTES = SD_WARPS * DEPTH * SD_ITEM_BYTES;
+    static constexpr int TILE_FLOATS = ROWS8 * 8 * SD_RED_PITCH;  // one warp's tile of one unit
+    static constexpr int RED_BYTES = 2 * SD_WARPS * TILE_FLOATS * 4;  // two units' tiles
+    static constexpr int BAR_BYTES = (SD_WARPS * DEPTH + 4) * 8 + 64;
+    static constexpr int SMEM_BYTES = 1024 + RING_BYTES + RED_BYTES + BAR_BYTES;
+    static_assert(SMEM_BYTES <= 232448, "streaming decode kernel: shared memory over the per-CTA limit");
+};
 
 // The blocks of all column tiles, in tile-major order, are cut into gridDim.x runs: with
 // q = blocks / CTAs and r = blocks % CTAs, the first r CTAs take q + 1 blocks and the rest q.
@@ -205,6 +213,9 @@ __device__ __forceinline__ void sd_epilogue(const W4Params& p, int nt, int row, 
 // HI: the product has more than 8 activation rows (rows 8..15 of the MMA tile are in use).
 template <bool HI>
 __global__ void __launch_bounds__(SD_THREADS, 1) w4a16_stream_kernel(const W4Params p) {
+    using Cfg = SdCfg<HI>;
+    constexpr int DEPTH = Cfg::DEPTH;
+    constexpr int ROWS = Cfg::ROWS8;
     extern __shared__ uint8_t sd_smem_raw[];
     const uint32_t raw_addr = smem_u32(sd_smem_raw);
     const uint32_t base = (raw_addr + 1023u) & ~1023u;
@@ -216,20 +227,24 @@ __global__ void __launch_bounds__(SD_THREADS, 1) w4a16_stream_kernel(const W4Par
     const int t = lane & 3;
     const int half = warp & 1;  // column half of the tile
     const int kl = warp >> 1;   // k-lane
-    constexpr int ROWS = HI ? 2 : 1;  // 8-row groups of the MMA tile in use
 
-    const int ring_off = warp * (SD_DEPTH * SD_ITEM_BYTES);
-    float* red = reinterpret_cast<float*>(base_ptr + SD_RING_BYTES);  // [warp][16][SD_RED_PITCH]
-    const uint32_t bars = base + SD_RING_BYTES + SD_RED_BYTES;
-    const uint32_t flag_slot = bars + SD_WARPS * SD_DEPTH * 8;
-    auto full = [&](int s) { return bars + static_cast<uint32_t>(warp * SD_DEPTH + s) * 8u; };
+    const int ring_off = warp * (DEPTH * SD_ITEM_BYTES);
+    // red[b][warp]: the warps' tiles of the units with parity b, [token row][column] with pitch SD_RED_PITCH
+    float* red = reinterpret_cast<float*>(base_ptr + Cfg::RING_BYTES);
+    const uint32_t bars = base + Cfg::RING_BYTES + Cfg::RED_BYTES;
+    auto full = [&](int s) { return bars + static_cast<uint32_t>(warp * DEPTH + s) * 8u; };
+    auto unit_done = [&](int b) { return bars + static_cast<uint32_t>(SD_WARPS * DEPTH + b) * 8u; };
+    auto reduced = [&](int b) { return bars + static_cast<uint32_t>(SD_WARPS * DEPTH + 2 + b) * 8u; };
+    const uint32_t flag_slot = bars + static_cast<uint32_t>(SD_WARPS * DEPTH + 4) * 8u;
 
-#ifdef SD_TIMING
-    unsigned long long* dbg = reinterpret_cast<unsigned long long*>(p.partials + static_cast<size_t>(p.n_tiles) * p.max_slices * 2048) + blockIdx.x * 8;
-    if (tid == 0) dbg[0] = globaltimer_ns();
-#endif
     if (lane == 0) {
-        for (int s = 0; s < SD_DEPTH; ++s) mbar_init(full(s), 1);
+        for (int s = 0; s < DEPTH; ++s) mbar_init(full(s), 1);
+        if (warp == 0) {
+            for (int b = 0; b < 2; ++b) {
+                mbar_init(unit_done(b), SD_WARPS);
+                mbar_init(reduced(b), SD_WARPS);
+            }
+        }
         fence_barrier_init();
         fence_proxy_async_smem();
     }
@@ -251,9 +266,9 @@ __global__ void __launch_bounds__(SD_THREADS, 1) w4a16_stream_kernel(const W4Par
     cur.nt = run.t0;
     cur.kb = run.b0 - run.t0 * kbt + kl;
     sd_normalize(cur, kbt);
-    SdPos pf = cur;  // the block SD_DEPTH items ahead
+    SdPos pf = cur;  // the block DEPTH items ahead
     int issued = 0;
-    for (int s = 0; s < SD_DEPTH; ++s) {
+    for (int s = 0; s < DEPTH; ++s) {
         if (issued < n_items) {
             if (lane == 0) request(pf, s);
             ++issued;
@@ -274,15 +289,76 @@ __global__ void __launch_bounds__(SD_THREADS, 1) w4a16_stream_kernel(const W4Par
     int it = 0;      // items this warp has consumed
     bool ok = true;  // false once a wait gave up
     const float zero4[4] = {0.f, 0.f, 0.f, 0.f};
+    const int c_out = tid & 63;  // output column (and column + 64) this thread sums
+    const int r_out = tid >> 6;  // output rows r_out, r_out + 8
+
+    // Adds the warps' tiles of unit v (parity v & 1) in lane order and writes the tile's output, or
+    // parks it in the workspace when other CTAs hold parts of the tile. Runs one unit late: by the
+    // time a warp gets here every warp has long flushed unit v, so nobody waits for the lane that
+    // happened to have one block more in that unit.
+    auto reduce_unit = [&](int v) {
+        SdUnit u;
+        sd_unit(p, run, v, u);
+        const int b = v & 1;
+        if (ok && !mbar_wait(unit_done(b), static_cast<uint32_t>(v >> 1) & 1u)) {
+            sd_report(p.status, warp, 10000 + v);
+            ok = false;
+        }
+        const float* tiles = red + b * (SD_WARPS * Cfg::TILE_FLOATS);
+        float vsum[ROWS][2];
+#pragma unroll
+        for (int i = 0; i < ROWS; ++i) {
+            const float* src = tiles + (r_out + 8 * i) * SD_RED_PITCH + c_out;
+            float a0 = 0.f, a1 = 0.f;
+#pragma unroll
+            for (int w = 0; w < SD_KLANES; ++w) {
+                a0 += src[(2 * w) * Cfg::TILE_FLOATS];
+                a1 += src[(2 * w + 1) * Cfg::TILE_FLOATS];
+            }
+            vsum[i][0] = a0;
+            vsum[i][1] = a1;
+        }
+        // this warp is done with the tiles of parity b
+        __syncwarp();
+        if (lane == 0) mbar_arrive(reduced(b));
+        if (u.kb0 == 0 && u.kb1 == p.kb_total) {
+#pragma unroll
+            for (int i = 0; i < ROWS; ++i) sd_epilogue(p, u.nt, r_out + 8 * i, c_out, vsum[i][0], vsum[i][1]);
+        } else {
+            // a tile shared with other CTAs: park the part in the workspace; the hand-over (fence,
+            // ticket, sum by the last CTA) waits until this CTA has streamed all its blocks, so the
+            // round trip to the L2 is paid once per CTA and not inside the stream
+            int sl, nsl;
+            sd_slices(p, run, u, sl, nsl);
+            float* part = p.partials + (static_cast<size_t>(u.nt) * p.max_slices + sl) * (16 * W4_TILE_N);
+#pragma unroll
+            for (int i = 0; i < ROWS; ++i) {
+                const int row = r_out + 8 * i;
+                if (row < p.M) {
+                    part[row * W4_TILE_N + c_out] = vsum[i][0];
+                    part[row * W4_TILE_N + c_out + 64] = vsum[i][1];
+                }
+            }
+            if (n_pending < 2) {
+                pend_nt[n_pending] = u.nt;
+                pend_nsl[n_pending] = nsl;
+            }
+            ++n_pending;
+        }
+    };
+
+    int n_units = 0;
     for (int ui = 0;; ++ui) {
         SdUnit u;
         if (!sd_unit(p, run, ui, u)) break;
+        n_units = ui + 1;
         // acc[o][jj]: tokens 8o .. 8o+7 (this lane: 2t, 2t+1) x columns 16jj+g ([0],[1]) and 16jj+8+g ([2],[3])
         float acc[ROWS][4][4];
 #pragma unroll
         for (int o = 0; o < ROWS; ++o)
 #pragma unroll
             for (int jj = 0; jj < 4; ++jj) acc[o][jj][0] = acc[o][jj][1] = acc[o][jj][2] = acc[o][jj][3] = 0.f;
+
 #pragma unroll 1
         while (it < n_items && cur.nt == u.nt) {
             const SdXFrag x = x_next;
@@ -295,8 +371,8 @@ __global__ void __launch_bounds__(SD_THREADS, 1) w4a16_stream_kernel(const W4Par
                 sd_load_x<HI>(p, xrow, nxt.kb, g, x_next);
                 sd_load_scales(p, nxt.nt * W4_TILE_N + half * 64 + lane, nxt.kb, sc0_next, sc1_next);
             }
-            const int s = it % SD_DEPTH;
-            const uint32_t ph = static_cast<uint32_t>(it / SD_DEPTH) & 1u;
+            const int s = it % DEPTH;
+            const uint32_t ph = static_cast<uint32_t>(it / DEPTH) & 1u;
             if (ok && !mbar_wait(full(s), ph)) {
                 sd_report(p.status, warp, it);
                 ok = false;
@@ -349,8 +425,13 @@ __global__ void __launch_bounds__(SD_THREADS, 1) w4a16_stream_kernel(const W4Par
             cur = nxt;
         }
 
-        // ---- add the k-lanes' tiles in lane order
-        float* mine = red + warp * (16 * SD_RED_PITCH);
+        // ---- flush this warp's tile of unit ui; the tiles of unit ui - 2 must have been added up
+        const int b = ui & 1;
+        if (ui >= 2 && ok && !mbar_wait(reduced(b), static_cast<uint32_t>((ui >> 1) - 1) & 1u)) {
+            sd_report(p.status, warp, 20000 + ui);
+            ok = false;
+        }
+        float* mine = red + (b * SD_WARPS + warp) * Cfg::TILE_FLOATS;
 #pragma unroll
         for (int o = 0; o < ROWS; ++o)
 #pragma unroll
@@ -361,63 +442,21 @@ __global__ void __launch_bounds__(SD_THREADS, 1) w4a16_stream_kernel(const W4Par
                 dst[8] = acc[o][jj][2];
                 dst[SD_RED_PITCH + 8] = acc[o][jj][3];
             }
-        __syncthreads();
-        const int c = tid & 63;
-        const int r0 = tid >> 6;  // 0..7
-        float v[ROWS][2];
-#pragma unroll
-        for (int i = 0; i < ROWS; ++i) {
-            const float* src = red + (r0 + 8 * i) * SD_RED_PITCH + c;
-            float a0 = 0.f, a1 = 0.f;
-#pragma unroll
-            for (int w = 0; w < SD_KLANES; ++w) {
-                a0 += src[(2 * w) * (16 * SD_RED_PITCH)];
-                a1 += src[(2 * w + 1) * (16 * SD_RED_PITCH)];
-            }
-            v[i][0] = a0;
-            v[i][1] = a1;
-        }
-        if (u.kb0 == 0 && u.kb1 == p.kb_total) {
-#pragma unroll
-            for (int i = 0; i < ROWS; ++i) sd_epilogue(p, u.nt, r0 + 8 * i, c, v[i][0], v[i][1]);
-        } else {
-            // a tile shared with other CTAs: park the part in the workspace; the hand-over (fence,
-            // ticket, sum by the last CTA) waits until this CTA has streamed all its blocks, so the
-            // round trip to the L2 is paid once per CTA and not inside the stream
-            int sl, nsl;
-            sd_slices(p, run, u, sl, nsl);
-            float* part = p.partials + (static_cast<size_t>(u.nt) * p.max_slices + sl) * (16 * W4_TILE_N);
-#pragma unroll
-            for (int i = 0; i < ROWS; ++i) {
-                const int row = r0 + 8 * i;
-                if (row < p.M) {
-                    part[row * W4_TILE_N + c] = v[i][0];
-                    part[row * W4_TILE_N + c + 64] = v[i][1];
-                }
-            }
-            if (n_pending < 2) {
-                pend_nt[n_pending] = u.nt;
-                pend_nsl[n_pending] = nsl;
-            }
-            ++n_pending;
-        }
-        __syncthreads();  // the lanes' tiles are reused by the next unit
+        __syncwarp();
+        if (lane == 0) mbar_arrive(unit_done(b));
+        if (ui >= 1) reduce_unit(ui - 1);
     }
+    if (n_units >= 1) reduce_unit(n_units - 1);
 
-#ifdef SD_TIMING
-    if (tid == 0) dbg[5] = globaltimer_ns();
-#endif
     // ---- hand-over of the shared tiles (only the first and the last tile of a run can be shared)
     if (n_pending > 2) {
         if (tid == 0) sd_report(p.status, -1, n_pending);
         n_pending = 2;
     }
-#ifdef SD_TIMING
-    if (n_pending == 0 && tid == 0) dbg[6] = globaltimer_ns();
-#endif
+    __syncthreads();  // all threads' partial sums are stored
     if (n_pending == 0) return;
-    // one release for the CTA: the barrier at the end of the last unit ordered all threads' stores
-    // before thread 0's gpu-scope fence, which is cumulative over them
+    // one release for the CTA: the barrier above ordered all threads' stores before thread 0's
+    // gpu-scope fence, which is cumulative over them
     if (tid == 0) {
         __threadfence();
         // both tickets are in flight together
@@ -430,8 +469,6 @@ __global__ void __launch_bounds__(SD_THREADS, 1) w4a16_stream_kernel(const W4Par
         }
     }
     __syncthreads();
-    const int c = tid & 63;
-    const int r0 = tid >> 6;
     for (int k = 0; k < n_pending; ++k) {
         uint32_t last;
         asm volatile("ld.shared.u32 %0, [%1];" : "=r"(last) : "r"(flag_slot + 4 * k) : "memory");
@@ -446,8 +483,8 @@ __global__ void __launch_bounds__(SD_THREADS, 1) w4a16_stream_kernel(const W4Par
             float q[ROWS][2];
 #pragma unroll
             for (int i = 0; i < ROWS; ++i) {
-                const int row = r0 + 8 * i;
-                const float* src = all + static_cast<size_t>(s2) * (16 * W4_TILE_N) + row * W4_TILE_N + c;
+                const int row = r_out + 8 * i;
+                const float* src = all + static_cast<size_t>(s2) * (16 * W4_TILE_N) + row * W4_TILE_N + c_out;
                 q[i][0] = row < p.M ? __ldcg(src) : 0.f;
                 q[i][1] = row < p.M ? __ldcg(src + 64) : 0.f;
             }
@@ -458,12 +495,8 @@ __global__ void __launch_bounds__(SD_THREADS, 1) w4a16_stream_kernel(const W4Par
             }
         }
 #pragma unroll
-        for (int i = 0; i < ROWS; ++i) sd_epilogue(p, pend_nt[k], r0 + 8 * i, c, sum[i][0], sum[i][1]);
+        for (int i = 0; i < ROWS; ++i) sd_epilogue(p, pend_nt[k], r_out + 8 * i, c_out, sum[i][0], sum[i][1]);
     }
-#ifdef SD_TIMING
-    __syncthreads();
-    if (tid == 0) dbg[6] = globaltimer_ns();
-#endif
 }
 
 W4StreamPlan w4_stream_plan(int N, int K, int sms) {
@@ -484,10 +517,10 @@ static int sd_launch(const W4Params& p, int grid, cudaStream_t stream) {
     WB_CHECK_CUDA(cudaGetDevice(&dev));
     if (dev >= 0 && dev < 64 && !attr_set[dev]) {
         WB_CHECK_CUDA(cudaFuncSetAttribute(w4a16_stream_kernel<HI>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                           SD_SMEM_BYTES));
+                                           SdCfg<HI>::SMEM_BYTES));
         attr_set[dev] = true;
     }
-    w4a16_stream_kernel<HI><<<grid, SD_THREADS, SD_SMEM_BYTES, stream>>>(p);
+    w4a16_stream_kernel<HI><<<grid, SD_THREADS, SdCfg<HI>::SMEM_BYTES, stream>>>(p);
     WB_CHECK_CUDA(cudaGetLastError());
     return WMMA_OPS_OK;
 }
