@@ -299,16 +299,6 @@ def measure_layer(w, dev, rank, world, steps):
         for _ in range(3):
             layer(x)
         ms = time_region(lambda: layer(x), max(3, min(steps, 10)), world, dev)
-        if label == "fp16_reduce":
-            # the same layer replayed from a CUDA graph (host launch overhead removed)
-            try:
-                replay, _, _ = layer.capture(x)
-                replay()
-                gms = time_region(replay, max(3, min(steps, 10)), world, dev)
-                out["fp16_reduce_cuda_graph"] = {"ms": gms, "tflops": olayer.layer_flops(tokens) / gms / 1e9,
-                                                 "tokens_per_s": tokens / gms * 1e3}
-            except Exception as e:  # capture of the collective is not available everywhere
-                out["fp16_reduce_cuda_graph"] = {"error": str(e)[:200]}
         out[label] = {"ms": ms, "tflops": olayer.layer_flops(tokens) / ms / 1e9, "tokens_per_s": tokens / ms * 1e3}
         del layer
     w.set_sm_margin(0)
@@ -325,8 +315,36 @@ def measure_layer(w, dev, rank, world, steps):
             out["fp16_reduce_nvswitch_multimem"] = {"ms": ms, "tflops": olayer.layer_flops(tokens) / ms / 1e9,
                                                     "tokens_per_s": tokens / ms * 1e3}
             del layer
+            # the same on token chunks: the reduction of one chunk (32 CTAs) runs beside the GEMMs
+            # of the next (148 - 32 SMs)
+            for chunks in (2, 4):
+                sw.max_ctas = 32
+                w.set_sm_margin(32)
+                layer = sharded.ShardedDecoderLinears(local, world=world, reduce_dtype=torch.float16, switch=sw,
+                                                      chunks=chunks)
+                for _ in range(3):
+                    layer(x)
+                ms = time_region(lambda: layer(x), max(3, min(steps, 10)), world, dev)
+                out[f"fp16_reduce_nvswitch_multimem_{chunks}chunks"] = {
+                    "ms": ms, "tflops": olayer.layer_flops(tokens) / ms / 1e9, "tokens_per_s": tokens / ms * 1e3}
+                del layer
+            w.set_sm_margin(0)
         except Exception as e:  # no symmetric memory / multicast on this system
             out["fp16_reduce_nvswitch_multimem"] = {"error": f"{type(e).__name__}: {str(e)[:200]}"}
+    # last, because capturing the collective changes how later eager collectives behave: the
+    # fp16-reduce layer replayed from a CUDA graph (host launch overhead removed)
+    try:
+        layer = sharded.ShardedDecoderLinears(local, world=world, reduce_dtype=torch.float16)
+        for _ in range(3):
+            layer(x)
+        replay, _, _ = layer.capture(x)
+        replay()
+        gms = time_region(replay, max(3, min(steps, 10)), world, dev)
+        out["fp16_reduce_cuda_graph"] = {"ms": gms, "tflops": olayer.layer_flops(tokens) / gms / 1e9,
+                                         "tokens_per_s": tokens / gms * 1e3}
+        del replay, layer
+    except Exception as e:  # capture of the collective is not available everywhere
+        out["fp16_reduce_cuda_graph"] = {"error": str(e)[:200]}
     best = max((r for r in out.values() if "tflops" in r), key=lambda r: r["tflops"])
     return {"workload": "llama7b_linears_w4a16_8192_tokens", "scaling": "strong", "n_gpus": world,
             "parallelism": f"tp{world}", "ms": best["ms"], "tflops": best["tflops"], "tokens_per_s": best["tokens_per_s"],

@@ -38,6 +38,28 @@ def main():
             e2 = og.rel_frobenius(mlp.float(), ref_mlp)
             print(f"world={world} reduce={rdt} attn_err={e1:.2e} mlp_err={e2:.2e}", flush=True)
             ok = ok and e1 < tol and e2 < 2 * tol
+    # the same layer with the partial outputs summed through the NVSwitch by the library's own
+    # multimem kernel (symmetric memory); skipped where the system offers no NVLink multicast
+    try:
+        from wmma_ops_b200.collective import SwitchAllReduce
+        sw = SwitchAllReduce(1024, 4096, dev)
+    except Exception as e:  # no symmetric memory / multicast
+        sw = None
+        if rank == 0:
+            print(f"switch all-reduce unavailable: {type(e).__name__}: {str(e)[:200]}", flush=True)
+    if sw is not None:
+        for chunks in (1, 2):
+            layer = sharded.ShardedDecoderLinears(local, world=world, reduce_dtype=torch.float16, chunks=chunks,
+                                                  switch=sw)
+            attn, mlp = layer(x.to(dev))
+            torch.cuda.synchronize()
+            w.check_status(dev)
+            if rank == 0:
+                ref_attn, ref_mlp = olayer.layer_ref(x, weights)
+                e1 = og.rel_frobenius(attn.float(), ref_attn)
+                e2 = og.rel_frobenius(mlp.float(), ref_mlp)
+                print(f"world={world} switch chunks={chunks} attn_err={e1:.2e} mlp_err={e2:.2e}", flush=True)
+                ok = ok and e1 < 3e-3 and e2 < 6e-3
     flag = torch.tensor([1 if ok else 0], device=dev)
     dist.broadcast(flag, 0)
     dist.barrier()

@@ -19,20 +19,36 @@
 
 namespace wb {
 
+__device__ __forceinline__ uint4 multimem_ld_reduce_f16(const uint4* p) {
+    uint4 v;
+    asm volatile("multimem.ld_reduce.relaxed.sys.global.add.acc::f32.v4.f16x2 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
+                 : "l"(p)
+                 : "memory");
+    return v;
+}
+
+__device__ __forceinline__ void multimem_st(uint4* p, const uint4& v) {
+    asm volatile("multimem.st.relaxed.sys.global.v4.f32 [%0], {%1,%2,%3,%4};" ::"l"(p), "r"(v.x), "r"(v.y), "r"(v.z),
+                 "r"(v.w)
+                 : "memory");
+}
+
+constexpr int AR_UNROLL = 8;  // reductions in flight per thread: a trip through the switch takes microseconds
+
 __global__ void __launch_bounds__(512) multimem_allreduce_f16_kernel(uint4* mc, size_t first_vec, size_t n_vec) {
     // mc: multicast address of the buffer; this rank reduces the 16-byte vectors [first_vec, first_vec + n_vec)
     const size_t stride = static_cast<size_t>(gridDim.x) * blockDim.x;
-    for (size_t i = static_cast<size_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < n_vec; i += stride) {
-        uint4* p = mc + first_vec + i;
-        uint32_t a, b, c, d;
-        asm volatile("multimem.ld_reduce.relaxed.sys.global.add.acc::f32.v4.f16x2 {%0,%1,%2,%3}, [%4];"
-                     : "=r"(a), "=r"(b), "=r"(c), "=r"(d)
-                     : "l"(p)
-                     : "memory");
-        asm volatile("multimem.st.relaxed.sys.global.v4.f32 [%0], {%1,%2,%3,%4};" ::"l"(p), "r"(a), "r"(b), "r"(c),
-                     "r"(d)
-                     : "memory");
+    uint4* base = mc + first_vec;
+    size_t i = static_cast<size_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+    for (; i + (AR_UNROLL - 1) * stride < n_vec; i += AR_UNROLL * stride) {
+        uint4 v[AR_UNROLL];
+#pragma unroll
+        for (int u = 0; u < AR_UNROLL; ++u) v[u] = multimem_ld_reduce_f16(base + i + u * stride);
+#pragma unroll
+        for (int u = 0; u < AR_UNROLL; ++u) multimem_st(base + i + u * stride, v[u]);
     }
+    for (; i < n_vec; i += stride) multimem_st(base + i, multimem_ld_reduce_f16(base + i));
     __threadfence_system();
 }
 

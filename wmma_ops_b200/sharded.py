@@ -202,8 +202,11 @@ class ShardedDecoderLinears:
         main = torch.cuda.current_stream(x.device)
         if getattr(self, "_streams", None) is None:
             self._streams = [torch.cuda.Stream(device=x.device) for _ in range(2)]
-        attn_out = torch.empty((T, self.packed["o"][1].shape[1]), dtype=out_dt, device=x.device)
-        mlp_out = torch.empty_like(attn_out)
+        if self.switch is not None:
+            attn_out, mlp_out = self.switch.buffer(0, T), self.switch.buffer(1, T)   # summed in place
+        else:
+            attn_out = torch.empty((T, self.packed["o"][1].shape[1]), dtype=out_dt, device=x.device)
+            mlp_out = torch.empty_like(attn_out)
         for st in self._streams:
             st.wait_stream(main)
         keep, stage1, stage2 = [], [], []
@@ -211,31 +214,48 @@ class ShardedDecoderLinears:
             with torch.cuda.stream(self._streams[c % 2]):
                 qkv16 = self._w4(x[a:b], "qkv", out_dtype=torch.float16, alpha=GLUE_SCALE)
                 o_in = qkv16[:, :self.q_cols].contiguous()
-                part = self._w4(o_in, "o", out_dtype=out_dt)
-                work = dist.all_reduce(part, op=dist.ReduceOp.SUM, async_op=True)
+                if self.switch is not None:
+                    # partial output into the symmetric buffer, summed through the switch by the
+                    # library's kernel on this side stream (a few CTAs; the other stream's GEMM
+                    # keeps the remaining SMs busy)
+                    self._w4(o_in, "o", out_dtype=torch.float16, out=self.switch.buffer(0)[a:b])
+                    part = self.switch.reduce(0, b - a, row0=a, channel=c % 2)
+                    work = None
+                else:
+                    part = self._w4(o_in, "o", out_dtype=out_dt)
+                    work = dist.all_reduce(part, op=dist.ReduceOp.SUM, async_op=True)
                 stage1.append((part, work))
                 keep += [qkv16, o_in]
         for c, (a, b) in enumerate(bounds):
             with torch.cuda.stream(self._streams[c % 2]):
                 part, work = stage1[c]
-                work.wait()
-                attn_out[a:b].copy_(part)
+                if work is not None:
+                    work.wait()
+                    attn_out[a:b].copy_(part)
                 h = (part * GLUE_SCALE).to(torch.float16)
                 act = self._w4(h, "gate_up", epilogue="silu_mul", alpha=GLUE_SCALE)
-                part2 = self._w4(act, "down", out_dtype=out_dt)
-                work2 = dist.all_reduce(part2, op=dist.ReduceOp.SUM, async_op=True)
+                if self.switch is not None:
+                    self._w4(act, "down", out_dtype=torch.float16, out=self.switch.buffer(1)[a:b])
+                    part2 = self.switch.reduce(1, b - a, row0=a, channel=2 + c % 2)
+                    work2 = None
+                else:
+                    part2 = self._w4(act, "down", out_dtype=out_dt)
+                    work2 = dist.all_reduce(part2, op=dist.ReduceOp.SUM, async_op=True)
                 stage2.append((part2, work2))
                 keep += [h, act]
         for c, (a, b) in enumerate(bounds):
             with torch.cuda.stream(self._streams[c % 2]):
                 part2, work2 = stage2[c]
-                work2.wait()
-                mlp_out[a:b].copy_(part2)
+                if work2 is not None:
+                    work2.wait()
+                    mlp_out[a:b].copy_(part2)
         for st in self._streams:
             main.wait_stream(st)
         # the intermediates were allocated on the side streams: tell the allocator the main stream
         # (which now depends on them) may still be using them
-        for t in keep + [p for p, _ in stage1] + [p for p, _ in stage2]:
+        if self.switch is None:
+            keep += [p for p, _ in stage1] + [p for p, _ in stage2]
+        for t in keep:
             t.record_stream(main)
         return attn_out, mlp_out
 
