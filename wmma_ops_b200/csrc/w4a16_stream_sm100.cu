@@ -237,6 +237,24 @@ __global__ void __launch_bounds__(SD_THREADS, 1) w4a16_stream_kernel(const W4Par
     auto reduced = [&](int b) { return bars + static_cast<uint32_t>(SD_WARPS * DEPTH + 2 + b) * 8u; };
     const uint32_t flag_slot = bars + static_cast<uint32_t>(SD_WARPS * DEPTH + 4) * 8u;
 
+    const SdRun run = sd_make_run(p);
+    const int kbt = p.kb_total;
+    const int nb = run.b1 - run.b0;
+    const int n_items = nb > kl ? (nb - kl + SD_KLANES - 1) / SD_KLANES : 0;  // this lane's blocks
+    SdPos cur;  // the block being consumed
+    cur.nt = run.t0;
+    cur.kb = run.b0 - run.t0 * kbt + kl;
+    sd_normalize(cur, kbt);
+    // The first item's activations and scales are requested before anything else: these first
+    // touches of X and of the scales take the longest of all the kernel's loads.
+    const __half* xrow = p.X + static_cast<size_t>(g) * p.K + 16 * t;
+    SdXFrag x_next;
+    uint32_t sc0_next = 0u, sc1_next = 0u;
+    if (n_items > 0) {
+        sd_load_x<HI>(p, xrow, cur.kb, g, x_next);
+        sd_load_scales(p, cur.nt * W4_TILE_N + half * 64 + lane, cur.kb, sc0_next, sc1_next);
+    }
+
     if (lane == 0) {
         for (int s = 0; s < DEPTH; ++s) mbar_init(full(s), 1);
         if (warp == 0) {
@@ -258,14 +276,6 @@ __global__ void __launch_bounds__(SD_THREADS, 1) w4a16_stream_kernel(const W4Par
         bulk_load_1d(base + ring_off + s * SD_ITEM_BYTES, src, SD_ITEM_BYTES, full(s));
     };
 
-    const SdRun run = sd_make_run(p);
-    const int kbt = p.kb_total;
-    const int nb = run.b1 - run.b0;
-    const int n_items = nb > kl ? (nb - kl + SD_KLANES - 1) / SD_KLANES : 0;  // this lane's blocks
-    SdPos cur;  // the block being consumed
-    cur.nt = run.t0;
-    cur.kb = run.b0 - run.t0 * kbt + kl;
-    sd_normalize(cur, kbt);
     SdPos pf = cur;  // the block DEPTH items ahead
     int issued = 0;
     for (int s = 0; s < DEPTH; ++s) {
@@ -276,14 +286,6 @@ __global__ void __launch_bounds__(SD_THREADS, 1) w4a16_stream_kernel(const W4Par
             sd_normalize(pf, kbt);
         }
     }
-    const __half* xrow = p.X + static_cast<size_t>(g) * p.K + 16 * t;
-    SdXFrag x_next;
-    uint32_t sc0_next = 0u, sc1_next = 0u;
-    if (n_items > 0) {
-        sd_load_x<HI>(p, xrow, cur.kb, g, x_next);
-        sd_load_scales(p, cur.nt * W4_TILE_N + half * 64 + lane, cur.kb, sc0_next, sc1_next);
-    }
-
     int pend_nt[2] = {0, 0}, pend_nsl[2] = {1, 1};  // shared tiles whose hand-over is still due
     int n_pending = 0;
     int it = 0;      // items this warp has consumed
@@ -479,20 +481,27 @@ __global__ void __launch_bounds__(SD_THREADS, 1) w4a16_stream_kernel(const W4Par
         float sum[ROWS][2];
 #pragma unroll
         for (int i = 0; i < ROWS; ++i) sum[i][0] = sum[i][1] = 0.f;
-        for (int s2 = 0; s2 < pend_nsl[k]; ++s2) {
-            float q[ROWS][2];
+        // four parts at a time, so that their loads (L2 round trips) are in flight together; the
+        // additions stay in CTA order
+        for (int s0 = 0; s0 < pend_nsl[k]; s0 += 4) {
+            float q[4][ROWS][2];
 #pragma unroll
-            for (int i = 0; i < ROWS; ++i) {
-                const int row = r_out + 8 * i;
-                const float* src = all + static_cast<size_t>(s2) * (16 * W4_TILE_N) + row * W4_TILE_N + c_out;
-                q[i][0] = row < p.M ? __ldcg(src) : 0.f;
-                q[i][1] = row < p.M ? __ldcg(src + 64) : 0.f;
-            }
+            for (int d2 = 0; d2 < 4; ++d2)
 #pragma unroll
-            for (int i = 0; i < ROWS; ++i) {
-                sum[i][0] += q[i][0];
-                sum[i][1] += q[i][1];
-            }
+                for (int i = 0; i < ROWS; ++i) {
+                    const int row = r_out + 8 * i;
+                    const bool on = s0 + d2 < pend_nsl[k] && row < p.M;
+                    const float* src = all + static_cast<size_t>(s0 + d2) * (16 * W4_TILE_N) + row * W4_TILE_N + c_out;
+                    q[d2][i][0] = on ? __ldcg(src) : 0.f;
+                    q[d2][i][1] = on ? __ldcg(src + 64) : 0.f;
+                }
+#pragma unroll
+            for (int d2 = 0; d2 < 4; ++d2)
+#pragma unroll
+                for (int i = 0; i < ROWS; ++i) {
+                    sum[i][0] += q[d2][i][0];
+                    sum[i][1] += q[d2][i][1];
+                }
         }
 #pragma unroll
         for (int i = 0; i < ROWS; ++i) sd_epilogue(p, pend_nt[k], r_out + 8 * i, c_out, sum[i][0], sum[i][1]);
