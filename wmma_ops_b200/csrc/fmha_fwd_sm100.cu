@@ -95,8 +95,10 @@ fmha_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
     auto s_full = [&](int s) { return bar_base + 8u * (9 + s); };
     auto s_empty = [&](int s) { return bar_base + 8u * (11 + s); };
     auto p_ready = [&](int s) { return bar_base + 8u * (13 + s); };
-    const uint32_t pv_done = bar_base + 8u * 15;
-    const uint32_t tmem_slot = bar_base + 8u * 16;
+    // P V of tile i reports to pv_done(i & 1): with two barriers a softmax thread that looks at
+    // tile i - 2 while working on tile i sees every phase of either barrier exactly once
+    auto pv_done = [&](int b) { return bar_base + 8u * (15 + b); };
+    const uint32_t tmem_slot = bar_base + 8u * 17;
 
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
@@ -120,7 +122,8 @@ fmha_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
             mbar_init(s_empty(s), 1);
             mbar_init(p_ready(s), 256);
         }
-        mbar_init(pv_done, 1);
+        mbar_init(pv_done(0), 1);
+        mbar_init(pv_done(1), 1);
         fence_barrier_init();
         fence_proxy_async_smem();
         prefetch_tmap(&tmap_q);
@@ -220,7 +223,7 @@ fmha_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
                 }
                 umma_commit(v_empty(s));
                 umma_commit(s_empty(s));
-                umma_commit(pv_done);
+                umma_commit(pv_done(s));
             }
         }
     } else {
@@ -241,6 +244,12 @@ fmha_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
         for (int i = 0; ok && i < n_tiles; ++i) {
             const int s = i & 1;
             const uint32_t ph = (i >> 1) & 1;
+            // look at P V of tile i - 2 (long finished): keeps this thread's view of pv_done(s) in step
+            if (i >= 2 && !mbar_wait(pv_done(s), ph ^ 1u)) {
+                fa_report(p.status, 2, 2000 + i);
+                ok = false;
+                break;
+            }
             if (!mbar_wait(s_full(s), ph)) {
                 fa_report(p.status, 2, i);
                 ok = false;
@@ -281,9 +290,15 @@ fmha_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
             named_barrier_sync(1, 256);
             float mx_other;
             asm volatile("ld.shared.f32 %0, [%1];" : "=f"(mx_other) : "r"(xchg + ((half ^ 1) * FA_BM + row) * 4) : "memory");
-            const float m_new = fmaxf(m_run, fmaxf(mx, mx_other));
+            // Lazy reference: the running maximum only moves when the tile's maximum exceeds it by more
+            // than 8 (in log2 units), so probabilities stay below 256 (fine in fp16, sums in fp32) and
+            // O is rescaled a few times per row instead of once per tile. Both halves of a row see the
+            // same maxima and take the same decision.
+            const float m_cand = fmaxf(m_run, fmaxf(mx, mx_other));
+            const bool move = (m_cand - m_run) > 8.f;  // false for -inf - -inf (NaN), true for x - -inf
+            const float m_new = move ? m_cand : m_run;
             const float m_safe = (m_new == -INFINITY) ? 0.f : m_new;
-            const float alpha = fast_exp2(m_run - m_safe);
+            const float alpha = move ? fast_exp2(m_run - m_safe) : 1.f;
 
             // probabilities -> fp16, written over the start of the S buffer (both halves have read
             // all of S before the barrier above): columns HC/2*half .. hold this half's keys
@@ -301,15 +316,15 @@ fmha_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
             l_run = l_run * alpha + sum;
             m_run = m_new;
 
-            if (i > 0) {
-                // O holds the sum through tile i-1; bring this half's columns to the new maximum
-                if (!mbar_wait(pv_done, (i - 1) & 1)) {
+            if (i > 0 && __any_sync(0xffffffffu, alpha != 1.f)) {
+                // O holds the sum through tile i-1; bring this half's columns to the new reference
+                if (!mbar_wait(pv_done(s ^ 1), static_cast<uint32_t>((i - 1) >> 1) & 1u)) {
                     fa_report(p.status, 2, 1000 + i);
                     ok = false;
                     break;
                 }
                 tc_fence_after_sync();
-                if (__any_sync(0xffffffffu, alpha != 1.f)) {
+                {
                     const uint32_t o_addr = tmem_base + Cfg::O_COL + lane_addr + half * (D / 2);
 #pragma unroll 1
                     for (int c = 0; c < D / 64; ++c) {
@@ -328,7 +343,7 @@ fmha_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
             named_barrier_sync(1, 256);  // the exchange slots are reused by the next tile
         }
         if (ok) {
-            if (!mbar_wait(pv_done, (n_tiles - 1) & 1)) {
+            if (!mbar_wait(pv_done((n_tiles - 1) & 1), static_cast<uint32_t>((n_tiles - 1) >> 1) & 1u)) {
                 fa_report(p.status, 2, -1);
                 ok = false;
             }
