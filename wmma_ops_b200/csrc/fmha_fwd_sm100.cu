@@ -33,7 +33,8 @@ struct FaCfg {
     static constexpr int Q_BOX_BYTES = FA_BM * 64 * 2;  // one [128 rows x 64 halves] box
     static constexpr int KV_TILE_BYTES = BN * D * 2;
     static constexpr int KV_BOX_BYTES = BN * 64 * 2;    // one [BN rows x 64 halves] box
-    static constexpr int XCHG_BYTES = 2 * FA_BM * 4;    // row maxima / sums passed between the two column halves
+    // row maxima (two sets, used by alternate key tiles) and row sums passed between the two column halves
+    static constexpr int XCHG_BYTES = 3 * 2 * FA_BM * 4;
     static constexpr int SMEM_BYTES = Q_TILE_BYTES + 4 * KV_TILE_BYTES + 1024 + 256 + XCHG_BYTES;
     static constexpr int S_COL0 = 0, S_COL1 = BN, O_COL = 2 * BN;
     static constexpr int TMEM_COLS = (2 * BN + D <= 256) ? 256 : 512;
@@ -86,7 +87,7 @@ fmha_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
     auto k_smem = [&](int s) { return smem_base + Cfg::Q_TILE_BYTES + s * Cfg::KV_TILE_BYTES; };
     auto v_smem = [&](int s) { return smem_base + Cfg::Q_TILE_BYTES + (2 + s) * Cfg::KV_TILE_BYTES; };
     const uint32_t bar_base = smem_base + Cfg::Q_TILE_BYTES + 4 * Cfg::KV_TILE_BYTES;
-    const uint32_t xchg = bar_base + 256u;  // [2 halves][128 rows] floats
+    const uint32_t xchg = bar_base + 256u;  // [3 sets][2 halves][128 rows] floats
     const uint32_t q_full = bar_base;
     auto k_full = [&](int s) { return bar_base + 8u * (1 + s); };
     auto k_empty = [&](int s) { return bar_base + 8u * (3 + s); };
@@ -286,10 +287,13 @@ fmha_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
             }
             float mx = fmaxf(mx0, mx1) * sl2;
             // exchange the row maximum with the other half
-            asm volatile("st.shared.f32 [%0], %1;" ::"r"(xchg + (half * FA_BM + row) * 4), "f"(mx) : "memory");
+            // set s of the exchange slots: it is written again two tiles on, after every thread has passed
+            // the next tile's barrier and so has read this tile's value
+            const uint32_t xs = xchg + s * (2 * FA_BM * 4);
+            asm volatile("st.shared.f32 [%0], %1;" ::"r"(xs + (half * FA_BM + row) * 4), "f"(mx) : "memory");
             named_barrier_sync(1, 256);
             float mx_other;
-            asm volatile("ld.shared.f32 %0, [%1];" : "=f"(mx_other) : "r"(xchg + ((half ^ 1) * FA_BM + row) * 4) : "memory");
+            asm volatile("ld.shared.f32 %0, [%1];" : "=f"(mx_other) : "r"(xs + ((half ^ 1) * FA_BM + row) * 4) : "memory");
             // Lazy reference: the running maximum only moves when the tile's maximum exceeds it by more
             // than 8 (in log2 units), so probabilities stay below 256 (fine in fp16, sums in fp32) and
             // O is rescaled a few times per row instead of once per tile. Both halves of a row see the
@@ -340,7 +344,6 @@ fmha_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
             tmem_wait_st();
             tc_fence_before_sync();
             mbar_arrive(p_ready(s));
-            named_barrier_sync(1, 256);  // the exchange slots are reused by the next tile
         }
         if (ok) {
             if (!mbar_wait(pv_done((n_tiles - 1) & 1), static_cast<uint32_t>((n_tiles - 1) >> 1) & 1u)) {
@@ -349,11 +352,12 @@ fmha_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
             }
         }
         // total row sum = sum of the two halves
-        asm volatile("st.shared.f32 [%0], %1;" ::"r"(xchg + (half * FA_BM + row) * 4), "f"(l_run) : "memory");
+        const uint32_t xl = xchg + 2 * (2 * FA_BM * 4);  // third set: the row sums
+        asm volatile("st.shared.f32 [%0], %1;" ::"r"(xl + (half * FA_BM + row) * 4), "f"(l_run) : "memory");
         named_barrier_sync(1, 256);
         if (ok) {
             float l_other;
-            asm volatile("ld.shared.f32 %0, [%1];" : "=f"(l_other) : "r"(xchg + ((half ^ 1) * FA_BM + row) * 4) : "memory");
+            asm volatile("ld.shared.f32 %0, [%1];" : "=f"(l_other) : "r"(xl + ((half ^ 1) * FA_BM + row) * 4) : "memory");
             tc_fence_after_sync();
             const float l_tot = l_run + l_other;
             const float inv = (l_tot > 0.f) ? 1.f / l_tot : 0.f;
