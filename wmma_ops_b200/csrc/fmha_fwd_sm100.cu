@@ -8,11 +8,11 @@
 // of 64 with an online softmax; two such CTAs share an SM:
 //   warp 0      TMA producer: Q once, then K and V tiles into two-stage rings
 //   warp 1      TMEM owner and issuer of S = Q K^T (fp32, TMEM)
-//   warp 10     issuer of O += P V (fp32, TMEM)
-//   warps 2..9  softmax: two warps per TMEM lane quadrant, each thread one query row and half of
-//               the tile's keys; read S from TMEM, keep the running max and sum, write P (fp16)
-//               back into tensor memory over S, from where P V reads it as its A operand,
-//               rescale O in TMEM when the max moved, and at the end store O / l as fp16.
+//   warp 6      issuer of O += P V (fp32, TMEM)
+//   warps 2..5  softmax, one thread per query row: read the row's 64 scores from TMEM, keep the
+//               row's reference maximum and sum, write P (fp16) back into tensor memory over the
+//               row's own scores, from where P V reads it as its A operand; rescale O in TMEM on
+//               the rare tiles where the reference moves, and at the end store O / l as fp16.
 // Two S accumulators let Q K^T of tile i+1 run on the tensor cores while the softmax warps
 // work on tile i. K is a K-major operand; V, read as [kv, d] with d contiguous,
 // is an MN-major operand, so neither is transposed.
@@ -22,7 +22,7 @@
 namespace wb {
 
 constexpr int FA_BM = 128;  // query rows per CTA
-constexpr int FA_THREADS = 352;  // warp 0 producer, warp 1 Q.K^T issuer, warps 2..9 softmax, warp 10 P.V issuer
+constexpr int FA_THREADS = 224;  // warp 0 producer, warp 1 Q.K^T issuer, warps 2..5 softmax, warp 6 P.V issuer
 
 // BN = keys per tile. BN = 64 keeps a CTA at 96 KB of shared memory and 256 TMEM columns (D = 128),
 // so two CTAs share an SM and one CTA's softmax latency hides behind the other's work.
@@ -33,9 +33,7 @@ struct FaCfg {
     static constexpr int Q_BOX_BYTES = FA_BM * 64 * 2;  // one [128 rows x 64 halves] box
     static constexpr int KV_TILE_BYTES = BN * D * 2;
     static constexpr int KV_BOX_BYTES = BN * 64 * 2;    // one [BN rows x 64 halves] box
-    // row maxima (two sets, used by alternate key tiles) and row sums passed between the two column halves
-    static constexpr int XCHG_BYTES = 3 * 2 * FA_BM * 4;
-    static constexpr int SMEM_BYTES = Q_TILE_BYTES + 4 * KV_TILE_BYTES + 1024 + 256 + XCHG_BYTES;
+    static constexpr int SMEM_BYTES = Q_TILE_BYTES + 4 * KV_TILE_BYTES + 1024 + 256;
     static constexpr int S_COL0 = 0, S_COL1 = BN, O_COL = 2 * BN;
     static constexpr int TMEM_COLS = (2 * BN + D <= 256) ? 256 : 512;
     static constexpr int CTAS_PER_SM = (TMEM_COLS == 256 && SMEM_BYTES <= 113 * 1024) ? 2 : 1;
@@ -87,7 +85,6 @@ fmha_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
     auto k_smem = [&](int s) { return smem_base + Cfg::Q_TILE_BYTES + s * Cfg::KV_TILE_BYTES; };
     auto v_smem = [&](int s) { return smem_base + Cfg::Q_TILE_BYTES + (2 + s) * Cfg::KV_TILE_BYTES; };
     const uint32_t bar_base = smem_base + Cfg::Q_TILE_BYTES + 4 * Cfg::KV_TILE_BYTES;
-    const uint32_t xchg = bar_base + 256u;  // [3 sets][2 halves][128 rows] floats
     const uint32_t q_full = bar_base;
     auto k_full = [&](int s) { return bar_base + 8u * (1 + s); };
     auto k_empty = [&](int s) { return bar_base + 8u * (3 + s); };
@@ -96,8 +93,11 @@ fmha_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
     auto s_full = [&](int s) { return bar_base + 8u * (9 + s); };
     auto s_empty = [&](int s) { return bar_base + 8u * (11 + s); };
     auto p_ready = [&](int s) { return bar_base + 8u * (13 + s); };
-    // P V of tile i reports to pv_done(i & 1): with two barriers a softmax thread that looks at
-    // tile i - 2 while working on tile i sees every phase of either barrier exactly once
+    // P V of tile i reports to pv_done(i & 1). A softmax thread waits on it only when it has to
+    // rescale O (tile i - 1's barrier, at tile i) and at the end. The parity wait is unambiguous
+    // without looking at every phase: at tile i, P V of tile i - 3 (the previous phase of that
+    // barrier) is known to be complete, because Q K^T of tile i - 1 could only be issued after it,
+    // and P V of tile i + 1 (the next phase) cannot complete before this thread has arrived for it.
     auto pv_done = [&](int b) { return bar_base + 8u * (15 + b); };
     const uint32_t tmem_slot = bar_base + 8u * 17;
 
@@ -121,7 +121,7 @@ fmha_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
             mbar_init(v_empty(s), 1);
             mbar_init(s_full(s), 1);
             mbar_init(s_empty(s), 1);
-            mbar_init(p_ready(s), 256);
+            mbar_init(p_ready(s), 128);
         }
         mbar_init(pv_done(0), 1);
         mbar_init(pv_done(1), 1);
@@ -201,7 +201,7 @@ fmha_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
                 umma_commit(s_full(s));
             }
         }
-    } else if (warp == 10) {
+    } else if (warp == 6) {
         // ------------------------------------------------------------ O += P V issuer
         if (lane == 0) {
             constexpr uint32_t idesc_o = make_idesc_f16_f32(FA_BM, D, false, true);
@@ -228,29 +228,22 @@ fmha_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
             }
         }
     } else {
-        // ------------------------------------------------------------ softmax warps (2..9)
-        // Two warps share each TMEM lane quadrant: warp (quad, half) owns the query rows
-        // 32*quad .. 32*quad+31 and the key columns 64*half .. 64*half+63 of every S tile, and the
-        // head-dim columns D/2*half .. of O. The halves exchange their row maxima through shared
-        // memory once per tile; the row sums are kept per half and added at the end.
+        // ------------------------------------------------------------ softmax warps (2..5)
+        // One thread per query row: warp w owns the TMEM lane quadrant w & 3, i.e. rows
+        // 32 (w & 3) .. + 31, and each of its threads all BN keys of a tile and all D columns of
+        // O. Nothing is exchanged between threads: a row's maximum, sum and probabilities live in
+        // one thread, and its P overwrites the row's own scores in tensor memory.
         const int quad = warp & 3;
-        const int half = (warp - 2) >> 2;
         const int row = quad * 32 + lane;
         const int q = q0 + row;
         const uint32_t lane_addr = static_cast<uint32_t>(quad * 32) << 16;
         const float sl2 = fmaxf(p.scale_log2, 1e-30f);  // > 0, so that -inf * sl2 stays -inf
-        float m_run = -INFINITY;  // running max of scale*log2e*s over both halves
-        float l_run = 0.f;        // running sum of exp2(.) over this half's columns
+        float m_run = -INFINITY;  // reference (scale * log2e * s units) the probabilities are taken against
+        float l_run = 0.f;        // running sum of exp2(.)
         bool ok = true;
         for (int i = 0; ok && i < n_tiles; ++i) {
             const int s = i & 1;
             const uint32_t ph = (i >> 1) & 1;
-            // look at P V of tile i - 2 (long finished): keeps this thread's view of pv_done(s) in step
-            if (i >= 2 && !mbar_wait(pv_done(s), ph ^ 1u)) {
-                fa_report(p.status, 2, 2000 + i);
-                ok = false;
-                break;
-            }
             if (!mbar_wait(s_full(s), ph)) {
                 fa_report(p.status, 2, i);
                 ok = false;
@@ -258,87 +251,80 @@ fmha_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
             }
             tc_fence_after_sync();
             const uint32_t s_addr = tmem_base + (s ? Cfg::S_COL1 : Cfg::S_COL0) + lane_addr;
-            constexpr int HC = FA_BN / 2;  // key columns per thread
-            const int kv0 = i * FA_BN + half * HC;
+            const int kv0 = i * FA_BN;
             const bool need_mask = (p.causal && i * FA_BN + FA_BN - 1 > q0) || (i * FA_BN + FA_BN > p.S);
             const int col_limit = p.causal ? min(p.S - 1, q) : p.S - 1;  // last visible key
 
-            // this half's raw scores, kept in registers (the scale is applied inside the exponent's
+            // the row's raw scores, kept in registers (the scale is applied inside the exponent's
             // FMA; it is positive, so the maximum can be taken on the raw scores)
-            float x[HC];
-#pragma unroll
-            for (int c = 0; c < HC / 32; ++c) {
-                uint32_t v[32];
-                tmem_ld_32x32b_x32(s_addr + half * HC + c * 32, v);
+            float x[FA_BN];
+            {
+                uint32_t v0[32], v1[32];  // both loads in flight before the one wait
+                tmem_ld_32x32b_x32(s_addr, v0);
+                tmem_ld_32x32b_x32(s_addr + 32, v1);
                 tmem_wait_ld();
 #pragma unroll
-                for (int j = 0; j < 32; ++j) x[c * 32 + j] = __uint_as_float(v[j]);
+                for (int j = 0; j < 32; ++j) {
+                    x[j] = __uint_as_float(v0[j]);
+                    x[32 + j] = __uint_as_float(v1[j]);
+                }
             }
             if (need_mask) {
 #pragma unroll
-                for (int j = 0; j < HC; ++j)
+                for (int j = 0; j < FA_BN; ++j)
                     if (kv0 + j > col_limit) x[j] = -INFINITY;
             }
-            float mx0 = -INFINITY, mx1 = -INFINITY;   // two chains of three-input maxima
+            float mx0 = -INFINITY, mx1 = -INFINITY, mx2 = -INFINITY, mx3 = -INFINITY;  // four chains of three-input maxima
 #pragma unroll
-            for (int j = 0; j < HC; j += 4) {
+            for (int j = 0; j < FA_BN; j += 8) {
                 mx0 = fmax3(mx0, x[j], x[j + 1]);
                 mx1 = fmax3(mx1, x[j + 2], x[j + 3]);
+                mx2 = fmax3(mx2, x[j + 4], x[j + 5]);
+                mx3 = fmax3(mx3, x[j + 6], x[j + 7]);
             }
-            float mx = fmaxf(mx0, mx1) * sl2;
-            // exchange the row maximum with the other half
-            // set s of the exchange slots: it is written again two tiles on, after every thread has passed
-            // the next tile's barrier and so has read this tile's value
-            const uint32_t xs = xchg + s * (2 * FA_BM * 4);
-            asm volatile("st.shared.f32 [%0], %1;" ::"r"(xs + (half * FA_BM + row) * 4), "f"(mx) : "memory");
-            named_barrier_sync(1, 256);
-            float mx_other;
-            asm volatile("ld.shared.f32 %0, [%1];" : "=f"(mx_other) : "r"(xs + ((half ^ 1) * FA_BM + row) * 4) : "memory");
-            // Lazy reference: the running maximum only moves when the tile's maximum exceeds it by more
-            // than 8 (in log2 units), so probabilities stay below 256 (fine in fp16, sums in fp32) and
-            // O is rescaled a few times per row instead of once per tile. Both halves of a row see the
-            // same maxima and take the same decision.
-            const float m_cand = fmaxf(m_run, fmaxf(mx, mx_other));
+            const float mx = fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3)) * sl2;
+            // Lazy reference: it only moves when the tile's maximum exceeds it by more than 8 (in log2
+            // units), so probabilities stay below 256 (fine in fp16, sums in fp32) and O is rescaled a
+            // few times per row instead of once per tile.
+            const float m_cand = fmaxf(m_run, mx);
             const bool move = (m_cand - m_run) > 8.f;  // false for -inf - -inf (NaN), true for x - -inf
             const float m_new = move ? m_cand : m_run;
             const float m_safe = (m_new == -INFINITY) ? 0.f : m_new;
             const float alpha = move ? fast_exp2(m_run - m_safe) : 1.f;
 
-            // probabilities -> fp16, written over the start of the S buffer (both halves have read
-            // all of S before the barrier above): columns HC/2*half .. hold this half's keys
-            float sum = 0.f;
-            uint32_t pk[HC / 2];
+            // probabilities -> fp16, written over the start of the row's own scores
+            float sum0 = 0.f, sum1 = 0.f;
+            uint32_t pk[FA_BN / 2];
 #pragma unroll
-            for (int j = 0; j < HC / 2; ++j) {
+            for (int j = 0; j < FA_BN / 2; ++j) {
                 const float e0 = fast_exp2(fmaf(x[2 * j], sl2, -m_safe));
                 const float e1 = fast_exp2(fmaf(x[2 * j + 1], sl2, -m_safe));
-                sum += e0 + e1;
+                sum0 += e0;
+                sum1 += e1;
                 pk[j] = pack_half2(e0, e1);
             }
-            if constexpr (HC == 64) tmem_st_32x32b_x32(s_addr + half * (HC / 2), pk);
-            else tmem_st_32x32b_x16(s_addr + half * (HC / 2), pk);
-            l_run = l_run * alpha + sum;
+            static_assert(FA_BN == 64, "the P store below is written for 64-key tiles");
+            tmem_st_32x32b_x32(s_addr, pk);
+            l_run = l_run * alpha + (sum0 + sum1);
             m_run = m_new;
 
             if (i > 0 && __any_sync(0xffffffffu, alpha != 1.f)) {
-                // O holds the sum through tile i-1; bring this half's columns to the new reference
+                // O holds the sum through tile i-1; bring the row to the new reference
                 if (!mbar_wait(pv_done(s ^ 1), static_cast<uint32_t>((i - 1) >> 1) & 1u)) {
                     fa_report(p.status, 2, 1000 + i);
                     ok = false;
                     break;
                 }
                 tc_fence_after_sync();
-                {
-                    const uint32_t o_addr = tmem_base + Cfg::O_COL + lane_addr + half * (D / 2);
+                const uint32_t o_addr = tmem_base + Cfg::O_COL + lane_addr;
 #pragma unroll 1
-                    for (int c = 0; c < D / 64; ++c) {
-                        uint32_t v[32];
-                        tmem_ld_32x32b_x32(o_addr + c * 32, v);
-                        tmem_wait_ld();
+                for (int c = 0; c < D / 32; ++c) {
+                    uint32_t v[32];
+                    tmem_ld_32x32b_x32(o_addr + c * 32, v);
+                    tmem_wait_ld();
 #pragma unroll
-                        for (int j = 0; j < 32; ++j) v[j] = __float_as_uint(__uint_as_float(v[j]) * alpha);
-                        tmem_st_32x32b_x32(o_addr + c * 32, v);
-                    }
+                    for (int j = 0; j < 32; ++j) v[j] = __float_as_uint(__uint_as_float(v[j]) * alpha);
+                    tmem_st_32x32b_x32(o_addr + c * 32, v);
                 }
             }
             tmem_wait_st();
@@ -351,20 +337,13 @@ fmha_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
                 ok = false;
             }
         }
-        // total row sum = sum of the two halves
-        const uint32_t xl = xchg + 2 * (2 * FA_BM * 4);  // third set: the row sums
-        asm volatile("st.shared.f32 [%0], %1;" ::"r"(xl + (half * FA_BM + row) * 4), "f"(l_run) : "memory");
-        named_barrier_sync(1, 256);
         if (ok) {
-            float l_other;
-            asm volatile("ld.shared.f32 %0, [%1];" : "=f"(l_other) : "r"(xl + ((half ^ 1) * FA_BM + row) * 4) : "memory");
             tc_fence_after_sync();
-            const float l_tot = l_run + l_other;
-            const float inv = (l_tot > 0.f) ? 1.f / l_tot : 0.f;
-            const uint32_t o_addr = tmem_base + Cfg::O_COL + lane_addr + half * (D / 2);
-            __half* out = p.O + (static_cast<size_t>(bh) * p.S + q) * D + half * (D / 2);
+            const float inv = (l_run > 0.f) ? 1.f / l_run : 0.f;
+            const uint32_t o_addr = tmem_base + Cfg::O_COL + lane_addr;
+            __half* out = p.O + (static_cast<size_t>(bh) * p.S + q) * D;
 #pragma unroll 1
-            for (int c = 0; c < D / 64; ++c) {
+            for (int c = 0; c < D / 32; ++c) {
                 uint32_t v[32];
                 tmem_ld_32x32b_x32(o_addr + c * 32, v);
                 tmem_wait_ld();
