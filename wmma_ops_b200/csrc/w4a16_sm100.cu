@@ -41,8 +41,13 @@ struct W4Cfg {
     static_assert(S * S_STAGE + R * W4_SLOT_BYTES + 1024 + 512 + 32 * 64 * 4 <= 232448, "shared memory budget");
     static constexpr int DQ = S;
     static_assert(R % S == 0 && DQ <= W4_DQ_WARPS, "ring sizes must nest");
+    // Threads that issue MMAs when the workers do not (prefill / mid-size token tiles): with two,
+    // alternate k-blocks go to warps 2 and 3, each with its own accumulator, which halves the
+    // chain of waits, MMAs and commits a single issuing thread has to walk per k-block. Two
+    // accumulators x two sets must fit the 512 TMEM columns, so token tiles up to 128 only.
+    static constexpr int NI = (!WM && BT >= 64 && BT <= 128) ? 2 : 1;
     // WM (worker-MMA, decode): every worker accumulates into its own BT columns, two sets
-    static constexpr int ACCS = WM ? DQ : 1;
+    static constexpr int ACCS = WM ? DQ : NI;
     static constexpr int TMEM_NEED = 2 * ACCS * BT;
     static constexpr int TMEM_COLS = TMEM_NEED <= 32 ? 32 : TMEM_NEED <= 64 ? 64 : TMEM_NEED <= 128 ? 128 : TMEM_NEED <= 256 ? 256 : 512;
     static_assert(TMEM_NEED <= 512, "TMEM budget");
@@ -92,7 +97,7 @@ w4a16_gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_const
             mbar_init(raw_full(r), 1);
         }
         for (int b = 0; b < 2; ++b) {
-            mbar_init(acc_full(b), WM ? Cfg::DQ : 1);
+            mbar_init(acc_full(b), WM ? Cfg::DQ : Cfg::NI);
             mbar_init(acc_empty(b), 128);
         }
         fence_barrier_init();
@@ -112,12 +117,14 @@ w4a16_gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_const
     asm volatile("ld.shared.u32 %0, [%1];" : "=r"(tmem_base) : "r"(tmem_slot) : "memory");
 
 
-    if (warp == 2) {
-        // ------------------------------------------------ MMA issuer
+    if (warp == 2 || (Cfg::NI == 2 && warp == 3)) {
+        // ------------------------------------------------ MMA issuer(s)
+        // Issuer q (warp 2 + q) takes the iterations j = q, q + NI, ... of the CTA's k-block
+        // sequence (stage j % S) and accumulates into its own accumulator of the current set.
         if (lane == 0 && !WM) {
             constexpr uint32_t idesc = make_idesc_f16_f32(W4_TILE_N, BT, false, false);
-            int s = 0;
-            uint32_t ph = 0;
+            const int q = warp - 2;
+            int j = 0;  // iteration index over all units of this CTA
             int acc = 0;
             uint32_t acc_ph = 0;
             bool ok = true;
@@ -129,8 +136,12 @@ w4a16_gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_const
                     break;
                 }
                 tc_fence_after_sync();
-                const uint32_t d_tmem = tmem_base + acc * BT;
-                for (int kb = kb0; kb < kb1; ++kb) {
+                const uint32_t d_tmem = tmem_base + (acc * Cfg::ACCS + q) * BT;
+                bool first = true;  // this issuer's first block of the unit overwrites its accumulator
+                for (int kb = kb0; kb < kb1; ++kb, ++j) {
+                    if (Cfg::NI == 2 && (j & 1) != q) continue;
+                    const int s = j % Cfg::S;
+                    const uint32_t ph = static_cast<uint32_t>(j / Cfg::S) & 1u;
                     if (!mbar_wait(x_full(s), ph) || !mbar_wait(wt_full(s), ph)) {
                         w4_report(p.status, 2, kb);
                         ok = false;
@@ -143,13 +154,10 @@ w4a16_gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_const
                     for (int kk = 0; kk < W4_BK / 16; ++kk) {
                         const uint64_t a_desc = make_smem_desc_sw128(wt_src + kk * 32, 16, 1024);
                         const uint64_t b_desc = make_smem_desc_sw128(x_src + kk * 32, 16, 1024);
-                        umma_f16(d_tmem, a_desc, b_desc, idesc, (kb > kb0 || kk > 0) ? 1u : 0u);
+                        umma_f16(d_tmem, a_desc, b_desc, idesc, (!first || kk > 0) ? 1u : 0u);
                     }
+                    first = false;
                     umma_commit(st_empty(s));
-                    if (++s == Cfg::S) {
-                        s = 0;
-                        ph ^= 1u;
-                    }
                 }
                 if (!ok) break;
                 umma_commit(acc_full(acc));
@@ -273,9 +281,16 @@ w4a16_gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_const
         const int et = threadIdx.x - 384;  // 0..127
         int acc = 0;
         uint32_t acc_ph = 0;
+        int j0 = 0;  // iteration index of the unit's first k-block (two issuers: which one had it)
         W4Unit U;
         for (int ui = 0; w4_unit(p, ui, U); ++ui) {
             const int nt = U.nt, tt = U.tt, sl = U.sl, nsl = U.nsl;
+            // with two MMA issuers, issuer q accumulated the unit's blocks with iteration parity q;
+            // a one-block unit leaves the other issuer's accumulator untouched (stale)
+            const int unit_blocks = U.kb1 - U.kb0;
+            const bool use0 = unit_blocks >= 2 || (j0 & 1) == 0;
+            const bool use1 = unit_blocks >= 2 || (j0 & 1) == 1;
+            j0 += unit_blocks;
             if (!mbar_wait_relaxed(acc_full(acc), acc_ph, 256)) {
                 w4_report(p.status, 4, ui);
                 break;
@@ -295,6 +310,18 @@ w4a16_gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_const
                 if constexpr (CH == 32) tmem_ld_32x32b_x32(t_addr + c * CH, v);
                 else tmem_ld_32x32b_x16(t_addr + c * CH, v);
                 tmem_wait_ld();
+                if constexpr (!WM && Cfg::NI == 2) {
+                    uint32_t u1[CH];
+                    if constexpr (CH == 32) tmem_ld_32x32b_x32(t_addr + BT + c * CH, u1);
+                    else tmem_ld_32x32b_x16(t_addr + BT + c * CH, u1);
+                    tmem_wait_ld();
+#pragma unroll
+                    for (int j = 0; j < CH; ++j) {
+                        const float a0 = use0 ? __uint_as_float(v[j]) : 0.f;
+                        const float a1 = use1 ? __uint_as_float(u1[j]) : 0.f;
+                        v[j] = __float_as_uint(a0 + a1);
+                    }
+                }
                 if constexpr (WM) {
                     // add the other workers' accumulators in worker order; the loads of two
                     // accumulators are in flight together
