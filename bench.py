@@ -329,6 +329,25 @@ def measure_layer(w, dev, rank, world, steps):
                     "ms": ms, "tflops": olayer.layer_flops(tokens) / ms / 1e9, "tokens_per_s": tokens / ms * 1e3}
                 del layer
             w.set_sm_margin(0)
+            # and replayed from CUDA graphs: at 4-8 GPUs the per-rank kernels are shorter than the
+            # Python launch path, which is what keeps the chunked form from overlapping anything
+            for chunks, ctas, margin in ((1, 0, 0), (2, 32, 32), (2, 16, 16)):
+                label = f"fp16_reduce_nvswitch_multimem_{chunks}chunks_ctas{ctas}_cuda_graph"
+                try:
+                    sw.max_ctas = ctas
+                    w.set_sm_margin(margin)
+                    layer = sharded.ShardedDecoderLinears(local, world=world, reduce_dtype=torch.float16, switch=sw,
+                                                          chunks=chunks)
+                    replay, _, _ = layer.capture(x)
+                    replay()
+                    gms = time_region(replay, max(3, min(steps, 10)), world, dev)
+                    out[label] = {"ms": gms, "tflops": olayer.layer_flops(tokens) / gms / 1e9,
+                                  "tokens_per_s": tokens / gms * 1e3}
+                    del replay, layer
+                except Exception as e:
+                    out[label] = {"error": f"{type(e).__name__}: {str(e)[:200]}"}
+            sw.max_ctas = 0
+            w.set_sm_margin(0)
         except Exception as e:  # no symmetric memory / multicast on this system
             out["fp16_reduce_nvswitch_multimem"] = {"error": f"{type(e).__name__}: {str(e)[:200]}"}
     # last, because capturing the collective changes how later eager collectives behave: the
