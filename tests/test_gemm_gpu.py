@@ -212,3 +212,27 @@ def test_linearity_and_full_size_property(cuda):
     assert ((rows - expect).norm() / expect.norm()).item() < 1e-4
     Ca = w.matmul_adaptive(A, B); _sync_ok()
     assert ((Ca - C).double().norm() / C.double().norm()).item() < 1e-5
+
+
+def test_matmul_host_pipelined_matches_device_matmul(cuda):
+    # pinned host operands, row blocks pipelined over three streams; same kernel, same K order
+    g = torch.Generator().manual_seed(41)
+    A = (torch.randn(1536, 512, generator=g) / 8).half().pin_memory()
+    B = torch.randn(512, 768, generator=g).half().pin_memory()
+    ref = w.matmul_adaptive(A.to(cuda), B.to(cuda)).cpu()
+    out = torch.empty((1536, 768), dtype=torch.float32).pin_memory()
+    for chunks in (1, 3, 6):
+        out.zero_()
+        got = w.matmul_host(A, B, out=out, chunks=chunks)
+        assert got is out
+        assert og.rel_frobenius(out, ref) < 1e-6
+    # back-to-back asynchronous calls reuse the two buffer sets correctly
+    outs = [torch.empty((1536, 768), dtype=torch.float32).pin_memory() for _ in range(4)]
+    for o in outs:
+        w.matmul_host(A, B, out=o, wait=False)
+    torch.cuda.synchronize()
+    w.check_status()
+    for o in outs:
+        assert torch.equal(o, outs[0]) and og.rel_frobenius(o, ref) < 1e-6
+    with pytest.raises(RuntimeError, match="pinned"):
+        w.matmul_host(A.clone(), B)

@@ -23,6 +23,7 @@ from .ops import (  # noqa: F401
     matmul_opt,
     matmul_pingpong,
     matmul_quad,
+    matmul_host,
     matmul_splitk,
     matmul_swizzled,
     matmul_tiled,

@@ -340,3 +340,93 @@ def gemm_inplace(A, B, C, alpha: float = 1.0, beta: float = 0.0) -> None:
     A, B = _finish_ab(A, B)
     _launch_gemm(A, B, C, C, M, N, K, alpha, beta, _DEFAULT_TILE, 1)
     return None
+
+
+# --------------------------------------------------------------------------- host-buffer GEMM
+class _HostGemmState:
+    """Device buffers, streams and events of matmul_host for one (device, M, N, K)."""
+
+    def __init__(self, dev: torch.device, M: int, N: int, K: int, chunks: int):
+        self.s_in = torch.cuda.Stream(device=dev)
+        self.s_mm = torch.cuda.Stream(device=dev)
+        self.s_out = torch.cuda.Stream(device=dev)
+        self.bufs = [(torch.empty((M, K), dtype=torch.float16, device=dev),
+                      torch.empty((K, N), dtype=torch.float16, device=dev),
+                      torch.empty((M, N), dtype=torch.float32, device=dev)) for _ in range(2)]
+        self.mm_done = [torch.cuda.Event() for _ in range(2)]    # the slot's A and B have been consumed
+        self.out_done = [torch.cuda.Event() for _ in range(2)]   # the slot's C has been copied out
+        self.ev_b = torch.cuda.Event()
+        self.ev_a = [torch.cuda.Event() for _ in range(chunks)]
+        self.ev_c = [torch.cuda.Event() for _ in range(chunks)]
+        self.calls = 0
+
+
+_host_gemm_states: dict = {}
+
+
+def matmul_host(A: torch.Tensor, B: torch.Tensor, out: Optional[torch.Tensor] = None, chunks: int = 8,
+                device: Optional[torch.device] = None, wait: bool = True) -> torch.Tensor:
+    """C = A @ B for operands that live in (pinned) host memory: fp16 A [M,K] and B [K,N] in,
+    fp32 C [M,N] out, also in pinned host memory. No counterpart in the reference (its callers
+    move tensors themselves); this is the end-to-end form of matmul_adaptive.
+
+    The copies and the GEMM are pipelined on three streams: B goes up first, then A in `chunks`
+    row blocks; the product of a row block starts as soon as the block has arrived, and its rows
+    of C go back down while the next block is still coming up, so the PCIe link is busy in both
+    directions at once. Two sets of device buffers let consecutive calls overlap as well.
+    A and B must be ready in host memory when the call is made. wait=False returns without
+    synchronising the host: the caller's current stream is made to wait for the result, so `out` is
+    complete for anything queued on that stream afterwards, or once that stream is synchronised."""
+    _require(not A.is_cuda and not B.is_cuda, "matmul_host takes host tensors")
+    _require(A.dtype == torch.float16 and B.dtype == torch.float16, "Inputs must be float16")
+    _require(A.dim() == 2 and B.dim() == 2, "Inputs must be 2D")
+    _require(A.size(1) == B.size(0), "Inner dimensions must match")
+    _require(A.is_contiguous() and B.is_contiguous(), "matmul_host: inputs must be contiguous")
+    _require(A.is_pinned() and B.is_pinned(), "matmul_host: inputs must be in pinned host memory")
+    M, K = A.shape
+    N = B.size(1)
+    if out is None:
+        out = torch.empty((M, N), dtype=torch.float32).pin_memory()
+    _require(not out.is_cuda and out.dtype == torch.float32 and tuple(out.shape) == (M, N) and out.is_contiguous()
+             and out.is_pinned(), "matmul_host: out must be a pinned, contiguous float32 host tensor [M, N]")
+    dev = torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)
+    _lib.load()
+    if M == 0 or N == 0:
+        return out
+    chunks = max(1, min(int(chunks), M // 256 if M >= 256 else 1))
+    key = (dev.index, M, N, K, chunks)
+    st = _host_gemm_states.get(key)
+    if st is None:
+        with torch.cuda.device(dev):
+            st = _HostGemmState(dev, M, N, K, chunks)
+        _host_gemm_states[key] = st
+    slot = st.calls & 1
+    st.calls += 1
+    dA, dB, dC = st.bufs[slot]
+    bounds = [(j * M // chunks, (j + 1) * M // chunks) for j in range(chunks)]
+    with torch.cuda.device(dev):
+        with torch.cuda.stream(st.s_in):
+            st.s_in.wait_event(st.mm_done[slot])       # the GEMMs that read this slot two calls ago
+            dB.copy_(B, non_blocking=True)
+            st.ev_b.record(st.s_in)
+            for j, (a, b) in enumerate(bounds):
+                dA[a:b].copy_(A[a:b], non_blocking=True)
+                st.ev_a[j].record(st.s_in)
+        with torch.cuda.stream(st.s_mm):
+            st.s_mm.wait_event(st.ev_b)
+            st.s_mm.wait_event(st.out_done[slot])      # this slot's C of two calls ago has left
+            for j, (a, b) in enumerate(bounds):
+                st.s_mm.wait_event(st.ev_a[j])
+                _launch_gemm(dA[a:b], dB, None, dC[a:b], b - a, N, K, 1.0, 0.0, _lib.TILE_AUTO, 0)
+                st.ev_c[j].record(st.s_mm)
+            st.mm_done[slot].record(st.s_mm)
+        with torch.cuda.stream(st.s_out):
+            for j, (a, b) in enumerate(bounds):
+                st.s_out.wait_event(st.ev_c[j])
+                out[a:b].copy_(dC[a:b], non_blocking=True)
+            st.out_done[slot].record(st.s_out)
+        # stream-ordered result: work queued on the caller's stream after this call sees `out` complete
+        torch.cuda.current_stream(dev).wait_event(st.out_done[slot])
+    if wait:
+        st.out_done[slot].synchronize()
+    return out
