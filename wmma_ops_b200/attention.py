@@ -6,7 +6,7 @@ from __future__ import annotations
 import torch
 
 from . import _lib
-from .ops import _post, _require, _status_word, _stream
+from .ops import _device_guard, _post, _require, _status_word, _stream
 
 
 def flash_attention(Q: torch.Tensor, K: torch.Tensor, V: torch.Tensor, causal: bool = False,
@@ -25,7 +25,7 @@ def flash_attention(Q: torch.Tensor, K: torch.Tensor, V: torch.Tensor, causal: b
     if Q.numel() == 0:
         return O
     dev = Q.device
-    with torch.cuda.device(dev):
+    with _device_guard(dev):
         rc = _lib.load().wmma_ops_fmha_fwd(Q.data_ptr(), K.data_ptr(), V.data_ptr(), O.data_ptr(), B, H, S, D,
                                            float(scale), 1 if causal else 0, _status_word(dev).data_ptr(), _stream(dev))
         _lib.check(rc)

@@ -54,6 +54,26 @@ def _workspace(device: torch.device, nbytes: int, zero_init: bool = False) -> to
     return t
 
 
+class _NullGuard:
+    def __enter__(self):
+        return None
+
+    def __exit__(self, *exc):
+        return False
+
+
+_NULL_GUARD = _NullGuard()
+
+
+def _device_guard(device: torch.device):
+    """torch.cuda.device(device), or nothing when it is the current device already (the context
+    manager costs a few microseconds per call, as much as a small kernel)."""
+    idx = device.index
+    if idx is None or idx == torch.cuda.current_device():
+        return _NULL_GUARD
+    return torch.cuda.device(device)
+
+
 def _stream(device: torch.device) -> int:
     return torch.cuda.current_stream(device).cuda_stream
 
@@ -106,7 +126,7 @@ def _check_c(C: torch.Tensor, A: torch.Tensor, M: int, N: int) -> None:
 def _launch_gemm(A, B, C_in, C_out, M, N, K, alpha, beta, tile_cfg, split_k) -> None:
     lib = _lib.load()
     dev = A.device
-    with torch.cuda.device(dev):
+    with _device_guard(dev):
         ws_ptr, ws_bytes = None, 0
         if tile_cfg == _lib.TILE_AUTO and split_k == 0 and M > 0 and N > 0 and K > 0:
             cfg, sk = select_tile(M, N, K, _sm_count(dev))

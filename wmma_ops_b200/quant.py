@@ -12,7 +12,7 @@ from typing import Optional, Tuple
 import torch
 
 from . import _lib
-from .ops import _post, _require, _sm_count, _status_word, _stream, _workspace
+from .ops import _device_guard, _post, _require, _sm_count, _status_word, _stream, _workspace
 
 ZERO_POINT = 8
 
@@ -40,7 +40,7 @@ def int4_prepack(codes: torch.Tensor, scales: torch.Tensor, group_size: int = 12
     codes = codes.contiguous()
     dev = codes.device
     q = torch.empty((K // 64, (N + 127) // 128, 128, 8), dtype=torch.int32, device=dev)
-    with torch.cuda.device(dev):
+    with _device_guard(dev):
         _lib.check(_lib.load().wmma_ops_int4_prepack(codes.data_ptr(), q.data_ptr(), K, N, _stream(dev)))
     return q, scales.contiguous()
 
@@ -58,7 +58,7 @@ def int4_unpack(qweight: torch.Tensor, N: int) -> torch.Tensor:
     K, N = _qshape(qweight, N)
     dev = qweight.device
     out = torch.empty((K, N), dtype=torch.uint8, device=dev)
-    with torch.cuda.device(dev):
+    with _device_guard(dev):
         _lib.check(_lib.load().wmma_ops_int4_unpack(qweight.data_ptr(), out.data_ptr(), K, N, _stream(dev)))
     return out
 
@@ -70,7 +70,7 @@ def int4_dequant(qweight: torch.Tensor, scales: torch.Tensor, group_size: int = 
     _require(scales.size(0) * group_size == K, "scales do not match K / group_size")
     dev = qweight.device
     out = torch.empty((K, N), dtype=torch.float16, device=dev)
-    with torch.cuda.device(dev):
+    with _device_guard(dev):
         _lib.check(_lib.load().wmma_ops_int4_dequant(qweight.data_ptr(), scales.contiguous().data_ptr(),
                                                      out.data_ptr(), K, N, group_size, _stream(dev)))
     return out
@@ -133,7 +133,7 @@ def matmul_w4a16(A: torch.Tensor, qweight: torch.Tensor, scales: torch.Tensor, g
         C = out
     if M == 0:
         return C
-    with torch.cuda.device(dev):
+    with _device_guard(dev):
         ws_ptr, ws_bytes = None, 0
         need = lib.wmma_ops_w4a16_workspace_bytes(M, N, K, split_k)   # split_k = 0: the library's own plan
         if need > 0:
