@@ -254,6 +254,19 @@ def measure_w4a16(w, dev, peaks, world):
         gbs, tf = by / ms / 1e6, 2.0 * M * N * K / ms / 1e9
         rows[f"M{M}"] = {"us": ms * 1e3, "gbs": gbs, "tflops": tf, "hbm_frac": gbs / peaks["hbm_gbs"],
                          "tensor_frac": tf / peaks["tflops"], "timed": "cuda graph replay" if M <= 128 else "eager launches"}
+        if M <= 16:
+            # the same with overlapped decode launches: each product's CTAs start fetching their
+            # weights while the previous product's last CTAs finish (programmatic dependent launch),
+            # which is how a decoder runs its layers back to back
+            w.set_w4a16_overlap(True)
+            try:
+                ms = _time_calls(fns, 10, world, dev, graph=True)
+                gbs, tf = by / ms / 1e6, 2.0 * M * N * K / ms / 1e9
+                rows[f"M{M}_overlapped_launches"] = {
+                    "us": ms * 1e3, "gbs": gbs, "tflops": tf, "hbm_frac": gbs / peaks["hbm_gbs"],
+                    "tensor_frac": tf / peaks["tflops"], "timed": "cuda graph replay, programmatic dependent launches"}
+            finally:
+                w.set_w4a16_overlap(False)
     return rows
 
 

@@ -117,6 +117,15 @@ int wmma_ops_int4_unpack(const void* qweight, void* codes_u8, int K, int N, void
 int wmma_ops_int4_dequant(const void* qweight, const void* scales, void* W_f16, int K, int N,
                           int group_size, void* stream);
 
+/* Overlapped decode launches (off by default; process-wide). When on, the streaming decode kernel
+ * (M <= 16, split_k = 0) is launched as a programmatic dependent launch: its CTAs may start, and
+ * request their first packed-weight blocks, while the previous kernel of the stream is still
+ * finishing; they wait for that kernel to complete before they read the activations or the
+ * scales or touch the workspace and the output. The caller promises that qweight is not written
+ * by the kernels queued just before the call (weights are static in decode). No counterpart in
+ * the reference. */
+int wmma_ops_set_w4a16_overlap(int enable);
+
 /* Bytes of scratch wmma_ops_w4a16_gemm needs for this shape and split_k (partial sums + arrival
  * counters); 0 when the plan has no partial sums. The buffer must be zero-filled once: the kernels
  * leave the counters (its first 64 KB) at zero, so one buffer can serve calls of any shape. */

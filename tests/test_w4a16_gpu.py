@@ -238,3 +238,33 @@ def test_streaming_decode_reuses_one_workspace_across_shapes(cuda):
         if shape in outs:
             assert torch.equal(C, outs[shape])      # deterministic across calls
         outs[shape] = C
+
+
+def test_streaming_decode_overlapped_launches(cuda):
+    # programmatic dependent launches: a product may start fetching its weights while the previous
+    # kernel finishes, but reads its activations (here: the previous product's output) only after
+    codes, scales = int4.seeded_w4(4096, 4096, 128, seed=41)
+    q, sc = w.int4_prepack(codes.to(cuda), scales.to(cuda), 128)
+    x0, _ = og.seeded_ab(4, 8, 4096, seed=42)
+    x0 = x0.to(cuda)
+    torch.cuda.synchronize()
+
+    def chain(n):
+        x = x0
+        for _ in range(n):
+            x = w.matmul_w4a16(x, q, sc, 128, out_dtype=torch.float16, alpha=0.02)
+        return x
+
+    ref = chain(6)
+    _sync_ok()
+    w.set_w4a16_overlap(True)
+    try:
+        for _ in range(4):
+            got = chain(6)
+            _sync_ok()
+            assert torch.equal(got, ref)
+        first = w.matmul_w4a16(x0, q, sc, 128)
+        _sync_ok()
+        assert og.rel_frobenius(first, int4.w4a16_ref(x0.cpu(), codes, scales, 128)) < TOL
+    finally:
+        w.set_w4a16_overlap(False)

@@ -43,6 +43,7 @@ SIGNATURES = {
     "wmma_ops_int4_prepack": (_c_int, [_vp, _vp, _c_int, _c_int, _vp]),
     "wmma_ops_int4_unpack": (_c_int, [_vp, _vp, _c_int, _c_int, _vp]),
     "wmma_ops_int4_dequant": (_c_int, [_vp, _vp, _vp, _c_int, _c_int, _c_int, _vp]),
+    "wmma_ops_set_w4a16_overlap": (_c_int, [_c_int]),
     "wmma_ops_w4a16_workspace_bytes": (_c_size_t, [_c_int, _c_int, _c_int, _c_int]),
     "wmma_ops_w4a16_select_split": (_c_int, [_c_int, _c_int, _c_int, _c_int]),
     "wmma_ops_w4a16_gemm": (_c_int, [_vp, _vp, _vp, _vp, _c_int, _c_int, _c_int, _c_int, _c_int, _vp,

@@ -227,6 +227,9 @@ __global__ void __launch_bounds__(SD_THREADS, 1) w4a16_stream_kernel(const W4Par
     const int t = lane & 3;
     const int half = warp & 1;  // column half of the tile
     const int kl = warp >> 1;   // k-lane
+    // let the next kernel of the stream start its own prologue as soon as SMs free up (it waits
+    // for this one to complete before it reads anything this one writes)
+    asm volatile("griddepcontrol.launch_dependents;");
 
     const int ring_off = warp * (DEPTH * SD_ITEM_BYTES);
     // red[b][warp]: the warps' tiles of the units with parity b, [token row][column] with pitch SD_RED_PITCH
@@ -245,16 +248,6 @@ __global__ void __launch_bounds__(SD_THREADS, 1) w4a16_stream_kernel(const W4Par
     cur.nt = run.t0;
     cur.kb = run.b0 - run.t0 * kbt + kl;
     sd_normalize(cur, kbt);
-    // The first item's activations and scales are requested before anything else: these first
-    // touches of X and of the scales take the longest of all the kernel's loads.
-    const __half* xrow = p.X + static_cast<size_t>(g) * p.K + 16 * t;
-    SdXFrag x_next;
-    uint32_t sc0_next = 0u, sc1_next = 0u;
-    if (n_items > 0) {
-        sd_load_x<HI>(p, xrow, cur.kb, g, x_next);
-        sd_load_scales(p, cur.nt * W4_TILE_N + half * 64 + lane, cur.kb, sc0_next, sc1_next);
-    }
-
     if (lane == 0) {
         for (int s = 0; s < DEPTH; ++s) mbar_init(full(s), 1);
         if (warp == 0) {
@@ -286,6 +279,21 @@ __global__ void __launch_bounds__(SD_THREADS, 1) w4a16_stream_kernel(const W4Par
             sd_normalize(pf, kbt);
         }
     }
+    // Everything above touches only the packed weights. When the caller has switched on
+    // overlapped decode launches (programmatic dependent launch; it then promises that the packed
+    // weights are not produced by the kernels just before this one), the CTA got here while the
+    // previous kernel was still finishing and its own weight blocks are already on their way. The
+    // activations, the scales, the workspace and the output are only touched once that kernel is
+    // complete. In an ordinary launch the wait returns at once.
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+    const __half* xrow = p.X + static_cast<size_t>(g) * p.K + 16 * t;
+    SdXFrag x_next;
+    uint32_t sc0_next = 0u, sc1_next = 0u;
+    if (n_items > 0) {
+        sd_load_x<HI>(p, xrow, cur.kb, g, x_next);
+        sd_load_scales(p, cur.nt * W4_TILE_N + half * 64 + lane, cur.kb, sc0_next, sc1_next);
+    }
+
     int pend_nt[2] = {0, 0}, pend_nsl[2] = {1, 1};  // shared tiles whose hand-over is still due
     int n_pending = 0;
     int it = 0;      // items this warp has consumed
@@ -519,6 +527,9 @@ W4StreamPlan w4_stream_plan(int N, int K, int sms) {
     return pl;
 }
 
+// 1: decode launches are programmatic dependent launches (set by wmma_ops_set_w4a16_overlap)
+static int g_w4_overlap = 0;
+
 template <bool HI>
 static int sd_launch(const W4Params& p, int grid, cudaStream_t stream) {
     static bool attr_set[64] = {};
@@ -529,8 +540,17 @@ static int sd_launch(const W4Params& p, int grid, cudaStream_t stream) {
                                            SdCfg<HI>::SMEM_BYTES));
         attr_set[dev] = true;
     }
-    w4a16_stream_kernel<HI><<<grid, SD_THREADS, SdCfg<HI>::SMEM_BYTES, stream>>>(p);
-    WB_CHECK_CUDA(cudaGetLastError());
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(grid);
+    cfg.blockDim = dim3(SD_THREADS);
+    cfg.dynamicSmemBytes = SdCfg<HI>::SMEM_BYTES;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = g_w4_overlap ? 1 : 0;
+    WB_CHECK_CUDA(cudaLaunchKernelEx(&cfg, w4a16_stream_kernel<HI>, p));
     return WMMA_OPS_OK;
 }
 
@@ -539,3 +559,8 @@ int w4_stream_launch(const W4Params& p, int grid, cudaStream_t stream) {
 }
 
 }  // namespace wb
+
+extern "C" int wmma_ops_set_w4a16_overlap(int enable) {
+    wb::g_w4_overlap = enable ? 1 : 0;
+    return WMMA_OPS_OK;
+}

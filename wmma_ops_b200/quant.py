@@ -79,6 +79,15 @@ def int4_dequant(qweight: torch.Tensor, scales: torch.Tensor, group_size: int = 
 OUT_F32, OUT_F16, OUT_F16_SILU_MUL = 0, 1, 2
 
 
+def set_w4a16_overlap(enable: bool) -> None:
+    """Switches overlapped decode launches on or off (off by default, process-wide): with it on,
+    matmul_w4a16 products with up to 16 rows start fetching their packed weights while the previous
+    kernel of the stream is still finishing (programmatic dependent launch) and wait for it before
+    reading the activations. Only for weights that are not produced by the kernels queued just
+    before the call, which is the case in decode."""
+    _lib.check(_lib.load().wmma_ops_set_w4a16_overlap(1 if enable else 0))
+
+
 def interleave_gate_up(codes: torch.Tensor, scales: torch.Tensor) -> Tuple[torch.Tensor, torch.Tensor]:
     """Reorders the columns of a [K, 2F] gate|up weight (gate columns first, then up columns) so that
     every 128-column tile holds 64 gate columns followed by the 64 up columns of the same outputs,
