@@ -7,8 +7,7 @@
 // One CTA owns 128 query rows of one (batch, head) and walks the key/value sequence in tiles
 // of 64 with an online softmax; two such CTAs share an SM:
 //   warp 0      TMA producer: Q once, then K and V tiles into two-stage rings
-//   warp 1      TMEM owner and issuer of S = Q K^T (fp32, TMEM)
-//   warp 6      issuer of O += P V (fp32, TMEM)
+//   warp 1      TMEM owner and issuer of both S = Q K^T and O += P V (fp32, TMEM)
 //   warps 2..5  softmax, one thread per query row: read the row's 64 scores from TMEM, keep the
 //               row's reference maximum and sum, write P (fp16) back into tensor memory over the
 //               row's own scores, from where P V reads it as its A operand; rescale O in TMEM on
@@ -22,7 +21,7 @@
 namespace wb {
 
 constexpr int FA_BM = 128;  // query rows per CTA
-constexpr int FA_THREADS = 224;  // warp 0 producer, warp 1 Q.K^T issuer, warps 2..5 softmax, warp 6 P.V issuer
+constexpr int FA_THREADS = 192;  // warp 0 producer, warp 1 MMA issuer, warps 2..5 softmax
 
 // BN = keys per tile. BN = 64 keeps a CTA at 96 KB of shared memory and 256 TMEM columns (D = 128),
 // so two CTAs share an SM and one CTA's softmax latency hides behind the other's work.
@@ -170,19 +169,44 @@ fmha_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
             }
         }
     } else if (warp == 1) {
-        // ------------------------------------------------------------ S = Q K^T issuer
-        // Two issuing threads (this one and warp 10 for P V): a single thread pays 40-75 ns per
-        // tcgen05.mma / commit / wait, about 20 of them per 64-key tile, which was longer than
-        // the tile's tensor time.
+        // ------------------------------------------------------------ MMA issuer
+        // One thread issues both products, in the order Q K^T(i), P V(i-1), Q K^T(i+1), ...
+        // tcgen05.mma operations of one thread execute in the order they were issued, so
+        // Q K^T(i+1), which overwrites the S buffer that holds P(i-1), may be issued right after
+        // P V(i-1) without waiting for it to complete. (With the two products issued by different
+        // threads that wait was needed, and the chain softmax(i-1) done -> P V(i-1) issued and
+        // complete -> Q K^T(i+1) issued and complete was longer than softmax(i): the softmax warps
+        // stood waiting for scores.)
         if (lane == 0) {
             constexpr uint32_t idesc_s = make_idesc_f16_f32(FA_BM, FA_BN, false, false);
+            constexpr uint32_t idesc_o = make_idesc_f16_f32(FA_BM, D, false, true);
             bool ok = mbar_wait(q_full, 0);
             if (!ok) fa_report(p.status, 1, -1);
+            auto issue_pv = [&](int i) -> bool {
+                const int s = i & 1;
+                const uint32_t ph = (i >> 1) & 1;
+                if (!mbar_wait(v_full(s), ph) || !mbar_wait(p_ready(s), ph)) {
+                    fa_report(p.status, 1, 1000 + i);
+                    return false;
+                }
+                tc_fence_after_sync();
+#pragma unroll
+                for (int kk = 0; kk < FA_BN / 16; ++kk) {
+                    // P (fp16, written by the softmax warps over the start of S buffer s) is the A
+                    // operand straight from tensor memory: 16 keys = 8 columns per MMA.
+                    // V: MN-major, 16 keys = 2048 bytes further; 64-wide d blocks KV_BOX_BYTES apart
+                    const uint64_t b_desc = make_smem_desc_sw128(v_smem(s) + kk * 2048, Cfg::KV_BOX_BYTES, 1024);
+                    umma_f16_ts(tmem_base + Cfg::O_COL, tmem_base + (s ? Cfg::S_COL1 : Cfg::S_COL0) + kk * 8, b_desc,
+                                idesc_o, (i > 0 || kk > 0) ? 1u : 0u);
+                }
+                umma_commit(v_empty(s));
+                umma_commit(pv_done(s));
+                return true;
+            };
             for (int i = 0; ok && i < n_tiles; ++i) {
                 const int s = i & 1;
                 const uint32_t ph = (i >> 1) & 1;
-                // S buffer s is free once P V of tile i-2 (which read P from it) has completed
-                if (!mbar_wait(k_full(s), ph) || !mbar_wait(s_empty(s), ph ^ 1u)) {
+                if (!mbar_wait(k_full(s), ph)) {
                     fa_report(p.status, 1, i);
                     ok = false;
                     break;
@@ -199,33 +223,9 @@ fmha_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
                 }
                 umma_commit(k_empty(s));
                 umma_commit(s_full(s));
+                if (i > 0) ok = issue_pv(i - 1);
             }
-        }
-    } else if (warp == 6) {
-        // ------------------------------------------------------------ O += P V issuer
-        if (lane == 0) {
-            constexpr uint32_t idesc_o = make_idesc_f16_f32(FA_BM, D, false, true);
-            for (int i = 0; i < n_tiles; ++i) {
-                const int s = i & 1;
-                const uint32_t ph = (i >> 1) & 1;
-                if (!mbar_wait(v_full(s), ph) || !mbar_wait(p_ready(s), ph)) {
-                    fa_report(p.status, 3, i);
-                    break;
-                }
-                tc_fence_after_sync();
-#pragma unroll
-                for (int kk = 0; kk < FA_BN / 16; ++kk) {
-                    // P (fp16, written by the softmax warps over the start of S buffer s) is the A
-                    // operand straight from tensor memory: 16 keys = 8 columns per MMA.
-                    // V: MN-major, 16 keys = 2048 bytes further; 64-wide d blocks KV_BOX_BYTES apart
-                    const uint64_t b_desc = make_smem_desc_sw128(v_smem(s) + kk * 2048, Cfg::KV_BOX_BYTES, 1024);
-                    umma_f16_ts(tmem_base + Cfg::O_COL, tmem_base + (s ? Cfg::S_COL1 : Cfg::S_COL0) + kk * 8, b_desc,
-                                idesc_o, (i > 0 || kk > 0) ? 1u : 0u);
-                }
-                umma_commit(v_empty(s));
-                umma_commit(s_empty(s));
-                umma_commit(pv_done(s));
-            }
+            if (ok && n_tiles > 0) issue_pv(n_tiles - 1);
         }
     } else {
         // ------------------------------------------------------------ softmax warps (2..5)
