@@ -89,7 +89,9 @@ w4a16_gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_const
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < Cfg::S; ++s) {
-            mbar_init(x_full(s), 1);
+            // without worker-issued MMAs one barrier per stage collects both the activation tile's
+            // bytes and the worker's "weights expanded" arrival: the MMA issuer then waits once per block
+            mbar_init(x_full(s), WM ? 1 : 2);
             mbar_init(wt_full(s), 1);
             mbar_init(st_empty(s), 1);
         }
@@ -142,7 +144,7 @@ w4a16_gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_const
                     if (Cfg::NI == 2 && (j & 1) != q) continue;
                     const int s = j % Cfg::S;
                     const uint32_t ph = static_cast<uint32_t>(j / Cfg::S) & 1u;
-                    if (!mbar_wait(x_full(s), ph) || !mbar_wait(wt_full(s), ph)) {
+                    if (!mbar_wait(x_full(s), ph)) {
                         w4_report(p.status, 2, kb);
                         ok = false;
                         break;
@@ -266,7 +268,7 @@ w4a16_gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_const
                         umma_commit(st_empty(s));
                         if (last) umma_commit(acc_full(set));
                     } else {
-                        mbar_arrive(wt_full(s));
+                        mbar_arrive(x_full(s));
                     }
                     if (pre.valid) request_raw(pre, j + Cfg::R);
                 }
