@@ -85,3 +85,26 @@ def test_gemm_argument_checks_need_no_gpu(lib):
     assert rc == _lib.ERR_INVALID and "16-byte aligned" in _lib.last_error()
     # empty output: nothing to do, no launch
     assert lib.wmma_ops_gemm_f16f32(None, None, None, None, 0, 8, 8, 1.0, 0.0, 0, 1, None, 0, None, None) == 0
+
+
+def test_w4a16_workspace_plan_of_the_streaming_decode_kernel():
+    # Pure host arithmetic (148 SMs assumed without a GPU): products with up to 16 rows and no explicit
+    # split get 64 KB of arrival counters plus, per 128-column tile, one 16 x 128 fp32 part for every
+    # CTA that can share the tile: ceil(k_blocks / shortest_run) + 1, shortest_run = blocks // CTAs.
+    lib = _lib.load()
+
+    def expect(N, K, sms=148):
+        n_tiles, kbt = -(-N // 128), K // 64
+        blocks = n_tiles * kbt
+        grid = min(sms, blocks)
+        per = blocks // grid
+        max_slices = -(-kbt // per) + 1
+        return 65536 + n_tiles * max_slices * 16 * 128 * 4
+
+    for (M, N, K) in [(1, 11008, 4096), (16, 11008, 4096), (16, 128, 64), (4, 4096, 11008), (8, 136, 512)]:
+        assert lib.wmma_ops_w4a16_workspace_bytes(M, N, K, 0) == expect(N, K)
+    # more rows, or an explicit split of 1: the tcgen05 kernel without partial sums
+    assert lib.wmma_ops_w4a16_workspace_bytes(17, 11008, 4096, 0) == 0
+    assert lib.wmma_ops_w4a16_workspace_bytes(16, 11008, 4096, 1) == 0
+    # the overlap switch is a plain setter
+    assert lib.wmma_ops_set_w4a16_overlap(1) == 0 and lib.wmma_ops_set_w4a16_overlap(0) == 0

@@ -12,14 +12,16 @@
 //     ring of SD_DEPTH shared-memory slots; its lane 0 refills a slot with one bulk copy as soon as
 //     the warp has finished the half block that was in it, so 64 copies per SM are in flight and
 //     no thread issues more than one copy per item;
-//   * a warp expands its half block straight into mma.sync B fragments in registers (the k order
-//     inside a fragment is chosen so that one 64-bit shared load per thread feeds four MMAs),
-//     multiplies X by the integer-valued fp16 weights code - 8 (exact) with fp32 accumulation
-//     and applies the group's fp16 scale to the fp32 sum of the block;
-//   * at the end of a run's part of a column tile the k-lanes' tiles are added in lane order in
-//     shared memory; if the tile is shared with other CTAs the sum goes to the workspace, and when
-//     the CTA has streamed all its blocks it takes a ticket per shared tile: the last CTA to arrive
-//     adds the parts in CTA order (deterministic) and writes the output.
+//   * a warp expands its half block straight into mma.sync A fragments in registers (the weights
+//     are the 16-row operand, the tokens the 8-column one; the k order inside a fragment is chosen
+//     so that one 64-bit shared load per thread feeds four MMAs and no operand is moved),
+//     multiplies by the integer-valued fp16 weights code - 8 (exact) with fp32 accumulation and
+//     applies the group's fp16 scale to the fp32 sum of the block;
+//   * the k-lanes' tiles of a column tile are added in lane order in shared memory, one tile late
+//     (double-buffered, so no CTA-wide barrier per tile); if the tile is shared with other CTAs
+//     the sum goes to the workspace, and when the CTA has streamed all its blocks it takes a
+//     ticket per shared tile: the last CTA to arrive adds the parts in CTA order (deterministic)
+//     and writes the output.
 //
 // Every mbarrier wait is bounded; a wait that gives up records {code 4, warp, block, detail} in the
 // status word and the CTA finishes its control flow without touching the data again.
