@@ -34,6 +34,31 @@ NCU_TRAFFIC_BYTES = {"gemm_8192": 1.33e9}
 
 
 # ----------------------------------------------------------------------------- helpers
+def w4a16_bytes(M: int, N: int, K: int, group_size: int = 128) -> int:
+    """Algorithmic bytes of one W4A16 product: packed weights + scales + activations + fp32 output."""
+    return K * N // 2 + 2 * (K // group_size) * N + 2 * M * K + 4 * M * N
+
+
+def fmha_flops(B: int, H: int, S: int, D: int, causal: bool) -> float:
+    return 4.0 * B * H * D * (S * (S + 1) / 2 if causal else S * S)
+
+
+def layer_flops(tokens: int, hidden: int = 4096, qkv_out: int = 12288, ffn: int = 11008) -> float:
+    return 2.0 * tokens * hidden * (qkv_out + hidden + 2 * ffn + ffn)
+
+
+def host_threads() -> int:
+    """Uses every host core for the CPU legs: launchers such as torch.distributed.run export
+    OMP_NUM_THREADS=1, which would time the host arm on one core."""
+    n = os.cpu_count() or 1
+    try:
+        n = len(os.sched_getaffinity(0))
+    except AttributeError:
+        pass
+    torch.set_num_threads(max(1, n))
+    return torch.get_num_threads()
+
+
 def load_peaks():
     p = ROOT / "MEASURED_PEAKS.json"
     if p.exists():
@@ -139,6 +164,7 @@ def cpu_gemm_sample(target_s: float = 10.0, seed: int = 0):
     """fp32 torch.matmul on the host cores on a row slice of the 8192^3 product.
     Returns (tflops, rows, seconds, threads)."""
     from oracle import gemm as og
+    host_threads()
     n = GEMM_N
     g = torch.Generator().manual_seed(seed)
     B = torch.randn(n, n, generator=g).half()
@@ -165,6 +191,8 @@ def run_reference_arm(args):
     if rank != 0:
         return
     from oracle import gemm as og
+    threads = host_threads()
+    print(f"reference arm: {threads} host threads (os.cpu_count() = {os.cpu_count()})", file=sys.stderr)
     n = GEMM_N
     g = torch.Generator().manual_seed(0)
     B = torch.randn(n, n, generator=g).half()
@@ -183,7 +211,6 @@ def run_reference_arm(args):
         og.gemm_ref(A, B)
     dt = (time.perf_counter() - t0) / args.steps
     tflops = 2.0 * rows * n * n / dt / 1e12
-    threads = torch.get_num_threads()
     sample = f"{rows} of {n} rows of A per step (fp32 torch.matmul on the host, inputs converted from fp16 each step)"
     print(json.dumps({
         "impl": "reference", "metric": "fp16_gemm_tflops_8192", "value": tflops, "unit": "TFLOP/s", "n_gpus": args.gpus,
@@ -235,7 +262,6 @@ def _time_calls(fns, iters, world, dev, graph=False):
 def measure_w4a16(w, dev, peaks, world):
     """W4A16 GEMM, K=4096, N=11008, group 128, M in {1,16,128,4096}: GB/s of algorithmic bytes and
     TFLOP/s. Eight distinct weight sets (8 x 23 MB > L2) are cycled so decode rows read HBM."""
-    from oracle import int4
     K, N, g = 4096, 11008, 128
     nbuf = 8
     gen = torch.Generator(device=dev).manual_seed(77)
@@ -250,7 +276,7 @@ def measure_w4a16(w, dev, peaks, world):
         A = torch.randn(M, K, generator=gen, device=dev).half()
         fns = [(lambda q=q, sc=sc: w.matmul_w4a16(A, q, sc, g)) for q, sc in weights]
         ms = _time_calls(fns, 3 if M > 128 else 10, world, dev, graph=M <= 128)
-        by = int4.w4a16_bytes(M, N, K, g)
+        by = w4a16_bytes(M, N, K, g)
         gbs, tf = by / ms / 1e6, 2.0 * M * N * K / ms / 1e9
         rows[f"M{M}"] = {"us": ms * 1e3, "gbs": gbs, "tflops": tf, "hbm_frac": gbs / peaks["hbm_gbs"],
                          "tensor_frac": tf / peaks["tflops"], "timed": "cuda graph replay" if M <= 128 else "eager launches"}
@@ -271,7 +297,6 @@ def measure_w4a16(w, dev, peaks, world):
 
 
 def measure_fmha(w, dev, peaks, world):
-    from oracle import attention as oa
     rows = {}
     gen = torch.Generator(device=dev).manual_seed(78)
     for S in (1024, 2048, 4096):
@@ -280,17 +305,24 @@ def measure_fmha(w, dev, peaks, world):
         V = torch.randn(4, 32, S, 128, generator=gen, device=dev).half()
         for causal in (False, True):
             ms = _time_calls([lambda: w.flash_attention(Q, Kt, V, causal)], 5, world, dev)
-            tf = oa.fmha_flops(4, 32, S, 128, causal) / ms / 1e9
+            tf = fmha_flops(4, 32, S, 128, causal) / ms / 1e9
             rows[f"S{S}_{'causal' if causal else 'full'}"] = {"ms": ms, "tflops": tf, "tensor_frac": tf / peaks["tflops"]}
     return rows
 
 
+LAYER_TOL = 1e-3   # relative Frobenius error against the fp32 oracle (the accuracy gate of the workload)
+
+
 def measure_layer(w, dev, rank, world, steps):
-    """Llama-7B-shaped W4A16 linears on 8192 tokens, column/row sharded over `world` ranks with
-    an NCCL all-reduce after O and down (strong scaling: the 8192 tokens are fixed)."""
+    """Llama-7B-shaped W4A16 linears on 8192 tokens, column/row sharded over `world` ranks with an
+    all-reduce after O and down (strong scaling: the 8192 tokens are fixed). Every timed variant is
+    also checked: the first 256 token rows of its outputs are compared with the CPU oracle of the
+    layer (rank 0 computes the oracle, every rank compares its own copy, the maximum is recorded).
+    `ms` is the fastest variant whose two errors are within LAYER_TOL."""
+    from oracle import gemm as og
     from oracle import layer as olayer
     from wmma_ops_b200 import sharded
-    tokens = 8192
+    tokens, sample = 8192, 256
     gen = torch.Generator(device=dev).manual_seed(99)   # same weights on every rank
     shapes = {"qkv": (4096, 12288), "o": (4096, 4096), "gate_up": (4096, 22016), "down": (11008, 4096)}
     full = {}
@@ -299,88 +331,110 @@ def measure_layer(w, dev, rank, world, steps):
         scales = (torch.rand(K // 128, N, generator=gen, device=dev) * 0.019 + 0.001).half()
         full[name] = (codes, scales)
     local = sharded.shard_layer_weights(full, rank, world)
-    del full
     x = torch.randn(tokens, 4096, generator=gen, device=dev).half()
-    out = {}
-    variants = (("fp32_reduce", torch.float32, 1, 0), ("fp16_reduce", torch.float16, 1, 0),
-                ("fp16_reduce_2chunks_margin16", torch.float16, 2, 16), ("fp16_reduce_4chunks_margin16", torch.float16, 4, 16))
-    for label, rdt, chunks, margin in variants:
-        if world == 1 and label not in ("fp32_reduce", "fp16_reduce"):
-            continue
-        w.set_sm_margin(margin)   # SMs left to NCCL so that it can overlap the persistent GEMMs
-        layer = sharded.ShardedDecoderLinears(local, world=world, reduce_dtype=rdt, chunks=chunks)
-        for _ in range(3):
-            layer(x)
-        ms = time_region(lambda: layer(x), max(3, min(steps, 10)), world, dev)
-        out[label] = {"ms": ms, "tflops": olayer.layer_flops(tokens) / ms / 1e9, "tokens_per_s": tokens / ms * 1e3}
-        del layer
-    w.set_sm_margin(0)
+    refs = torch.empty((2, sample, 4096), dtype=torch.float32, device=dev)
+    if rank == 0:
+        host_threads()
+        ra, rm = olayer.layer_ref(x[:sample].cpu(), {k: (c.cpu(), sc.cpu()) for k, (c, sc) in full.items()})
+        refs[0].copy_(ra)
+        refs[1].copy_(rm)
+    del full
     if world > 1:
-        # partial outputs written into symmetric memory and summed through the NVSwitch by the
-        # library's own multimem kernel instead of NCCL
+        import torch.distributed as dist
+        dist.broadcast(refs, 0)
+    flops = layer_flops(tokens)
+    out = {}
+
+    def record(label, run, outputs, note=None):
+        """Times `run` and checks the outputs it leaves in `outputs()` against the oracle rows."""
         try:
-            from wmma_ops_b200.collective import SwitchAllReduce
-            sw = SwitchAllReduce(tokens, 4096, dev)
-            layer = sharded.ShardedDecoderLinears(local, world=world, reduce_dtype=torch.float16, switch=sw)
             for _ in range(3):
-                layer(x)
-            ms = time_region(lambda: layer(x), max(3, min(steps, 10)), world, dev)
-            out["fp16_reduce_nvswitch_multimem"] = {"ms": ms, "tflops": olayer.layer_flops(tokens) / ms / 1e9,
-                                                    "tokens_per_s": tokens / ms * 1e3}
+                run()
+            ms = time_region(run, max(3, min(steps, 10)), world, dev)
+            attn, mlp = outputs()
+            torch.cuda.synchronize()
+            errs = torch.tensor([og.rel_frobenius(attn[:sample].float().cpu(), refs[0].cpu()),
+                                 og.rel_frobenius(mlp[:sample].float().cpu(), refs[1].cpu())], dtype=torch.float64, device=dev)
+            if world > 1:
+                dist.all_reduce(errs, op=dist.ReduceOp.MAX)
+            e = errs.tolist()
+            row = {"ms": ms, "tflops": flops / ms / 1e9, "tokens_per_s": tokens / ms * 1e3, "attn_err": e[0], "mlp_err": e[1],
+                   "within_tol": bool(e[0] <= LAYER_TOL and e[1] <= LAYER_TOL)}
+            if note:
+                row["note"] = note
+            out[label] = row
+        except Exception as e:  # a variant that is not available on this system
+            out[label] = {"error": f"{type(e).__name__}: {str(e)[:200]}"}
+
+    def eager(layer):
+        last = {}
+
+        def run():
+            last["o"] = layer(x)
+        return run, (lambda: last["o"])
+
+    def graphed(layer):
+        replay, attn, mlp = layer.capture(x)
+        return replay, (lambda: (attn, mlp))
+
+    if world == 1:
+        layer = sharded.ShardedDecoderLinears(local, world=1)
+        record("single_gpu", *eager(layer))
+    else:
+        from wmma_ops_b200.collective import SwitchAllReduce
+        for label, rdt in (("nccl_fp32_reduce", torch.float32), ("nccl_fp16_reduce", torch.float16)):
+            layer = sharded.ShardedDecoderLinears(local, world=world, reduce_dtype=rdt)
+            record(label, *eager(layer))
             del layer
-            # the same on token chunks: the reduction of one chunk (32 CTAs) runs beside the GEMMs
-            # of the next (148 - 32 SMs)
-            for chunks in (2, 4):
-                sw.max_ctas = 32
-                w.set_sm_margin(32)
-                layer = sharded.ShardedDecoderLinears(local, world=world, reduce_dtype=torch.float16, switch=sw,
-                                                      chunks=chunks)
-                for _ in range(3):
-                    layer(x)
-                ms = time_region(lambda: layer(x), max(3, min(steps, 10)), world, dev)
-                out[f"fp16_reduce_nvswitch_multimem_{chunks}chunks"] = {
-                    "ms": ms, "tflops": olayer.layer_flops(tokens) / ms / 1e9, "tokens_per_s": tokens / ms * 1e3}
-                del layer
-            w.set_sm_margin(0)
-            # and replayed from CUDA graphs: at 4-8 GPUs the per-rank kernels are shorter than the
-            # Python launch path, which is what keeps the chunked form from overlapping anything
-            for chunks, ctas, margin in ((1, 0, 0), (2, 32, 32), (2, 16, 16)):
-                label = f"fp16_reduce_nvswitch_multimem_{chunks}chunks_ctas{ctas}_cuda_graph"
+        sw = None
+        try:
+            sw = SwitchAllReduce(tokens, 4096, dev)
+        except Exception as e:  # no symmetric memory / multicast on this system
+            out["nvswitch"] = {"error": f"{type(e).__name__}: {str(e)[:200]}"}
+        if sw is not None:
+            # partial outputs written into symmetric memory by the row-parallel GEMMs and summed
+            # through the NVSwitch by the library's own kernel (barriers inside the kernel)
+            for label, part in (("nvswitch_fp16_partials", torch.float16), ("nvswitch_fp32_partials", torch.float32)):
                 try:
-                    sw.max_ctas = ctas
-                    w.set_sm_margin(margin)
-                    layer = sharded.ShardedDecoderLinears(local, world=world, reduce_dtype=torch.float16, switch=sw,
-                                                          chunks=chunks)
-                    replay, _, _ = layer.capture(x)
-                    replay()
-                    gms = time_region(replay, max(3, min(steps, 10)), world, dev)
-                    out[label] = {"ms": gms, "tflops": olayer.layer_flops(tokens) / gms / 1e9,
-                                  "tokens_per_s": tokens / gms * 1e3}
-                    del replay, layer
+                    layer = sharded.ShardedDecoderLinears(local, world=world, reduce_dtype=part, switch=sw)
                 except Exception as e:
                     out[label] = {"error": f"{type(e).__name__}: {str(e)[:200]}"}
-            sw.max_ctas = 0
-            w.set_sm_margin(0)
-        except Exception as e:  # no symmetric memory / multicast on this system
-            out["fp16_reduce_nvswitch_multimem"] = {"error": f"{type(e).__name__}: {str(e)[:200]}"}
-    # last, because capturing the collective changes how later eager collectives behave: the
-    # fp16-reduce layer replayed from a CUDA graph (host launch overhead removed)
-    try:
-        layer = sharded.ShardedDecoderLinears(local, world=world, reduce_dtype=torch.float16)
-        for _ in range(3):
-            layer(x)
-        replay, _, _ = layer.capture(x)
-        replay()
-        gms = time_region(replay, max(3, min(steps, 10)), world, dev)
-        out["fp16_reduce_cuda_graph"] = {"ms": gms, "tflops": olayer.layer_flops(tokens) / gms / 1e9,
-                                         "tokens_per_s": tokens / gms * 1e3}
-        del replay, layer
-    except Exception as e:  # capture of the collective is not available everywhere
-        out["fp16_reduce_cuda_graph"] = {"error": str(e)[:200]}
-    best = max((r for r in out.values() if "tflops" in r), key=lambda r: r["tflops"])
-    return {"workload": "llama7b_linears_w4a16_8192_tokens", "scaling": "strong", "n_gpus": world,
-            "parallelism": f"tp{world}", "ms": best["ms"], "tflops": best["tflops"], "tokens_per_s": best["tokens_per_s"],
-            "variants": out}
+                    continue
+                record(label, *eager(layer))
+                # replayed from a CUDA graph: at 4-8 GPUs the per-rank kernels are shorter than the host
+                # needs to launch them one by one
+                try:
+                    run, outs = graphed(layer)
+                    record(label + "_cuda_graph", run, outs)
+                    del run, outs
+                except Exception as e:
+                    out[label + "_cuda_graph"] = {"error": f"{type(e).__name__}: {str(e)[:200]}"}
+                del layer
+        # last, because capturing NCCL collectives changes how later eager collectives behave
+        try:
+            layer = sharded.ShardedDecoderLinears(local, world=world, reduce_dtype=torch.float16)
+            for _ in range(2):
+                layer(x)
+            run, outs = graphed(layer)
+            record("nccl_fp16_reduce_cuda_graph", run, outs)
+            del run, outs, layer
+        except Exception as e:
+            out["nccl_fp16_reduce_cuda_graph"] = {"error": f"{type(e).__name__}: {str(e)[:200]}"}
+    timed = [r for r in out.values() if "ms" in r]
+    good = [r for r in timed if r["within_tol"]]
+    best = min(good or timed, key=lambda r: r["ms"])
+    res = {"workload": "llama7b_linears_w4a16_8192_tokens", "scaling": "strong", "n_gpus": world,
+           "parallelism": f"tp{world}", "ms": best["ms"], "tflops": best["tflops"], "tokens_per_s": best["tokens_per_s"],
+           "variant": next(k for k, r in out.items() if r is best), "attn_err": best["attn_err"], "mlp_err": best["mlp_err"],
+           "tolerance": LAYER_TOL, "checked": f"first {sample} token rows of both outputs against the CPU oracle, max over ranks",
+           "variants": out}
+    if world > 1:
+        # bytes each GPU must send (and receive) for the two sums of one layer: every rank's partial
+        # [tokens, 4096] leaves once and the summed result comes back once, minus the local 1/world
+        elem = 2
+        res["nvlink"] = {"min_bytes_per_gpu_per_layer": int(2 * 2 * tokens * 4096 * elem * (world - 1) / world),
+                         "note": "fp16 partials and sums; fp32 partials double the outgoing half"}
+    return res
 
 
 def cpu_side_baselines():
@@ -389,7 +443,7 @@ def cpu_side_baselines():
     from oracle import attention as oa
     from oracle import int4
     from oracle import layer as olayer
-    threads = torch.get_num_threads()
+    threads = host_threads()
     out = {}
     K, N = 4096, 11008
     codes, scales = int4.seeded_w4(K, N, 128, seed=7)
@@ -400,20 +454,20 @@ def cpu_side_baselines():
         int4.w4a16_ref(A, codes, scales, 128)
         dt = time.perf_counter() - t0
         out[f"w4a16_M{M}"] = {"ms": dt * 1e3, "tflops": 2.0 * M * N * K / dt / 1e12,
-                              "gbs": int4.w4a16_bytes(M, N, K, 128) / dt / 1e9, "cores": threads, "kind": "port",
+                              "gbs": w4a16_bytes(M, N, K, 128) / dt / 1e9, "cores": threads, "kind": "port",
                               "sample": f"full product at M={M}: dequantise 4096x11008 to fp16, then fp32 matmul"}
     Q, Kt, V = oa.seeded_qkv(1, 2, 2048, 128, seed=9)
     t0 = time.perf_counter()
     oa.attention_ref(Q, Kt, V, False)
     dt = time.perf_counter() - t0
-    out["fmha_S2048"] = {"ms": dt * 1e3, "tflops": oa.fmha_flops(1, 2, 2048, 128, False) / dt / 1e12, "cores": threads,
+    out["fmha_S2048"] = {"ms": dt * 1e3, "tflops": fmha_flops(1, 2, 2048, 128, False) / dt / 1e12, "cores": threads,
                          "kind": "port", "sample": "2 of the 128 (batch, head) pairs at S=2048, non-causal"}
     weights = olayer.make_layer_weights(seed=21)
     x = torch.randn(256, 4096, generator=g).half()
     t0 = time.perf_counter()
     olayer.layer_ref(x, weights)
     dt = time.perf_counter() - t0
-    out["layer"] = {"ms": dt * 1e3, "tflops": olayer.layer_flops(256) / dt / 1e12, "cores": threads, "kind": "port",
+    out["layer"] = {"ms": dt * 1e3, "tflops": layer_flops(256) / dt / 1e12, "cores": threads, "kind": "port",
                     "sample": "256 of the 8192 tokens through the four dequantised linears"}
     return out
 
@@ -438,8 +492,11 @@ def run_ours(args):
     dev = torch.device("cuda", local_rank)
     torch.cuda.set_device(dev)
     if world > 1:
-        # stdout carries exactly one JSON line: keep NCCL's version banner off it
-        os.environ["NCCL_DEBUG"] = "WARN"
+        # stdout carries exactly one JSON line; NCCL's communicator lines (ranks, transport, NVLS)
+        # are wanted as a record of the run, so they go to stderr
+        os.environ.setdefault("NCCL_DEBUG", "INFO")
+        os.environ.setdefault("NCCL_DEBUG_SUBSYS", "INIT")
+        os.environ.setdefault("NCCL_DEBUG_FILE", "/dev/stderr")
         import torch.distributed as dist
         dist.init_process_group("nccl", device_id=dev)
     peaks = load_peaks()

@@ -117,18 +117,26 @@ int wmma_ops_int4_unpack(const void* qweight, void* codes_u8, int K, int N, void
 int wmma_ops_int4_dequant(const void* qweight, const void* scales, void* W_f16, int K, int N,
                           int group_size, void* stream);
 
-/* Overlapped decode launches (off by default; process-wide). When on, the streaming decode kernel
+/* Overlapped decode launches (off by default; process-wide). When on, the decode kernel
  * (M <= 16, split_k = 0) is launched as a programmatic dependent launch: its CTAs may start, and
- * request their first packed-weight blocks, while the previous kernel of the stream is still
+ * request their packed-weight segments, while the previous kernel of the stream is still
  * finishing; they wait for that kernel to complete before they read the activations or the
- * scales or touch the workspace and the output. The caller promises that qweight is not written
- * by the kernels queued just before the call (weights are static in decode). No counterpart in
- * the reference. */
+ * scales or touch the output. The caller promises that qweight is not written by the kernels
+ * queued just before the call (weights are static in decode). No counterpart in the reference. */
 int wmma_ops_set_w4a16_overlap(int enable);
 
+/* The decode kernel's launch plan for an M x N x K product (M <= 16), host arithmetic only:
+ * plan[0..10] = {grid, clusters, ksplit, units, groups_per_unit, units_per_chunk, ring_depth,
+ * slot_bytes, reduction_pitch, shared_memory_bytes, groups_per_chunk_of_the_kernel_variant}. Columns are dealt in units of 16 (pairs of a
+ * gate and an up group with WMMA_OPS_W4_OUT_F16_SILU_MUL) to `clusters` clusters of `ksplit` CTAs;
+ * the CTAs of a cluster split K. num_sms <= 0: 148. No counterpart in the reference. */
+int wmma_ops_w4a16_decode_plan(int M, int N, int K, int out_mode, int num_sms, int* plan);
+
 /* Bytes of scratch wmma_ops_w4a16_gemm needs for this shape and split_k (partial sums + arrival
- * counters); 0 when the plan has no partial sums. The buffer must be zero-filled once: the kernels
- * leave the counters (its first 64 KB) at zero, so one buffer can serve calls of any shape. */
+ * counters of the tcgen05 kernel's split plans); 0 when the plan has no partial sums, which includes
+ * every product the decode kernel takes (M <= 16, split_k = 0). The buffer must be zero-filled
+ * once: the kernels leave the counters (its first 64 KB) at zero, so one buffer can serve calls of
+ * any shape; after a non-zero status word, zero it again before the next call. */
 size_t wmma_ops_w4a16_workspace_bytes(int M, int N, int K, int split_k);
 
 /* Split-K factor wmma_ops_w4a16_gemm picks when split_k == 0 and M > 16. */
@@ -138,13 +146,16 @@ int wmma_ops_w4a16_select_split(int M, int N, int K, int num_sms);
  * kernel, never materialised in global memory.
  * Requirements: K % 64 == 0, K % group_size == 0, group_size % 64 == 0, N % 8 == 0.
  * split_k: 0 = the library's plan, 1 = none, > 1 = that many K slices (needs workspace).
- * With split_k == 0 and M <= 16 (decode) the product runs on the streaming kernel: every SM
- * streams an equal share of the packed weights, column tiles shared by several CTAs are summed in
- * CTA order by the last CTA to finish (deterministic), and it always needs the workspace. That
- * kernel multiplies by the exact integers code - 8 and applies the fp16 group scale to the fp32
- * sum of each 64-deep block, so its result differs from "dequantise to fp16, then multiply" by
- * the fp16 rounding of the weights (about 2e-4 relative); the tcgen05 kernel used otherwise
- * multiplies by the fp16-rounded weights of wmma_ops_int4_dequant. */
+ * Arithmetic contract: weight[k][n] = (code - 8) * scale[k / group_size][n] exactly, fp16
+ * activations, fp32 accumulation; the result is within 1e-3 (relative Frobenius) of that product.
+ * Two kernels implement it and differ in where the fp16 scale is applied:
+ *   M > 16 or split_k != 0  the tcgen05 kernel multiplies by the fp16-rounded weights of
+ *          wmma_ops_int4_dequant (one rounding per weight, about 2e-4 relative);
+ *   M <= 16 and split_k == 0  the decode kernel multiplies by the exact integers code - 8 and
+ *          applies the scale to the fp32 sum of each 64-deep block (no weight rounding; half of
+ *          the zero points are removed by a constant-operand MMA chain, 5e-7 relative). Every CTA
+ *          owns a range of columns and walks all of K, sums are added in a fixed order
+ *          (deterministic), and no workspace is needed. */
 int wmma_ops_w4a16_gemm(const void* A, const void* qweight, const void* scales, void* C, int M,
                         int N, int K, int group_size, int split_k, void* workspace,
                         size_t workspace_bytes, int* status, void* stream);
@@ -180,6 +191,18 @@ int wmma_ops_multimem_allreduce_f16(void* multicast_ptr, size_t n_halves, int ra
  * scale < 0 means 1/sqrt(D). Requirements: D == 128 or D == 64, S >= 1. */
 int wmma_ops_fmha_fwd(const void* Q, const void* K, const void* V, void* O, int B, int H, int S,
                       int D, float scale, int causal, int* status, void* stream);
+
+/* Self-tests of the failure reporting (no counterpart in the reference, whose kernels have no
+ * bounded waits). wmma_ops_selftest_wait_expiry launches one tiny kernel whose only wait is on a
+ * barrier nobody arrives at; after limit_cycles SM cycles (1e3 .. 4e9) the wait gives up, the
+ * kernel returns normally and status reads {7, 77, 0, detail}. wmma_ops_selftest_debug_index
+ * evaluates the debug build's index check on `index` against a buffer of n ints: in range, the
+ * kernel writes out[index] = 1; out of range, the store is skipped and, in the debug build only,
+ * status reads {9, 104, 0, index}. wmma_ops_debug_checks_enabled returns 1 for the library built
+ * with -DWMMA_OPS_DEBUG_CHECKS (device-side index checks that write the status word), else 0. */
+int wmma_ops_selftest_wait_expiry(long long limit_cycles, int detail, int* status, void* stream);
+int wmma_ops_selftest_debug_index(int index, int n, int* out, int* status, void* stream);
+int wmma_ops_debug_checks_enabled(void);
 
 #ifdef __cplusplus
 }

@@ -68,6 +68,23 @@ def w4a16_ref(A: torch.Tensor, codes: torch.Tensor, scales: torch.Tensor, group_
     return torch.matmul(A.detach().cpu().float(), W.float())
 
 
+def w4a16_block_scaled_ref(A: torch.Tensor, codes: torch.Tensor, scales: torch.Tensor, group_size: int = 128) -> torch.Tensor:
+    """The decode kernel's own definition of the product (M <= 16, library-chosen plan): no weight
+    is rounded; C[m, n] = sum over 64-deep blocks b of scale[b*64 // g, n] * sum_{k in b} A[m, k] *
+    (code[k, n] - 8). Evaluated in float64 (the integer-weighted block sums are exact there), returned
+    as fp32. It differs from w4a16_ref, which rounds every (code - 8) * scale product to fp16 first,
+    by that rounding (about 2e-4 relative)."""
+    K, N = codes.shape
+    a = A.detach().cpu().to(torch.float64)
+    q = (codes.detach().cpu().to(torch.int32) - ZERO_POINT).to(torch.float64)
+    s = scales.detach().cpu().to(torch.float64)
+    out = torch.zeros(a.shape[0], N, dtype=torch.float64)
+    for b in range(K // 64):
+        blk = a[:, 64 * b:64 * b + 64] @ q[64 * b:64 * b + 64]
+        out += blk * s[(64 * b) // group_size][None, :]
+    return out.to(torch.float32)
+
+
 def seeded_w4(K: int, N: int, group_size: int = 128, seed: int = 7):
     """codes uniform in [0,15], scales fp16 uniform in [0.001, 0.02] (the W4A16 config)."""
     g = torch.Generator().manual_seed(seed)

@@ -98,6 +98,25 @@ def test_config4_full_size_properties(cuda, S):
     assert og.rel_frobenius(part.float(), ref.float()) < REL_TOL
 
 
+@pytest.mark.parametrize("S", [2048, 4096])
+def test_config4_causal_long_sequences_against_oracle(cuda, S):
+    # B=4, H=32, D=128 at the two long sequence lengths, causal and not, against the fp32 oracle on two
+    # (batch, head) pairs each (the oracle materialises S x S scores per head)
+    Q, K, V = oa.seeded_qkv(4, 32, S, 128, seed=70 + S)
+    Qd, Kd, Vd = Q.to(cuda), K.to(cuda), V.to(cuda)
+    for causal in (True, False):
+        O = w.flash_attention(Qd, Kd, Vd, causal=causal)
+        torch.cuda.synchronize()
+        w.check_status()
+        for b, h in [(0, 3), (3, 30)]:
+            ref = oa.attention_ref(Q[b:b + 1, h:h + 1], K[b:b + 1, h:h + 1], V[b:b + 1, h:h + 1], causal)
+            got = O[b:b + 1, h:h + 1].float()
+            err = og.rel_frobenius(got, ref.float())
+            print(f"S={S} causal={causal} (b={b}, h={h}): rel {err:.2e} max-abs {(got.cpu() - ref.float()).abs().max().item():.2e}")
+            assert err < REL_TOL
+            assert (got.cpu() - ref.float()).abs().max().item() < ABS_TOL
+
+
 def test_errors(cuda):
     Q = torch.randn(1, 2, 64, 128, device=cuda).half()
     with pytest.raises(RuntimeError, match="Inputs must be float16"):

@@ -87,24 +87,87 @@ def test_gemm_argument_checks_need_no_gpu(lib):
     assert lib.wmma_ops_gemm_f16f32(None, None, None, None, 0, 8, 8, 1.0, 0.0, 0, 1, None, 0, None, None) == 0
 
 
-def test_w4a16_workspace_plan_of_the_streaming_decode_kernel():
-    # Pure host arithmetic (148 SMs assumed without a GPU): products with up to 16 rows and no explicit
-    # split get 64 KB of arrival counters plus, per 128-column tile, one 16 x 128 fp32 part for every
-    # CTA that can share the tile: ceil(k_blocks / shortest_run) + 1, shortest_run = blocks // CTAs.
-    lib = _lib.load()
+def _decode_plan(lib, M, N, K, mode=0, sms=148):
+    out = (ctypes.c_int * 11)()
+    assert lib.wmma_ops_w4a16_decode_plan(M, N, K, mode, sms, out) == 0, _lib.last_error()
+    keys = ("grid", "clusters", "ksplit", "units", "gpu", "upc", "depth", "slot_bytes", "pitch", "smem_bytes", "ncg")
+    return dict(zip(keys, list(out)))
 
-    def expect(N, K, sms=148):
-        n_tiles, kbt = -(-N // 128), K // 64
-        blocks = n_tiles * kbt
-        grid = min(sms, blocks)
-        per = blocks // grid
-        max_slices = -(-kbt // per) + 1
-        return 65536 + n_tiles * max_slices * 16 * 128 * 4
 
-    for (M, N, K) in [(1, 11008, 4096), (16, 11008, 4096), (16, 128, 64), (4, 4096, 11008), (8, 136, 512)]:
-        assert lib.wmma_ops_w4a16_workspace_bytes(M, N, K, 0) == expect(N, K)
-    # more rows, or an explicit split of 1: the tcgen05 kernel without partial sums
+def _group_col(gu, v0, j):
+    # column of group j of a chunk that starts at unit v0 (the kernel's sc_group_col)
+    if not gu:
+        return (v0 + j) * 16
+    v = v0 + j // 2
+    return (v // 4) * 128 + (v % 4) * 16 + (j % 2) * 64
+
+
+@pytest.mark.parametrize("case", [
+    (1, 11008, 4096, 0), (16, 11008, 4096, 0), (8, 4096, 11008, 0), (16, 4096, 4096, 0), (3, 22016, 4096, 0),
+    (16, 128, 64, 0), (2, 8, 64, 0), (5, 136, 512, 0), (16, 40000, 64, 0), (9, 1000, 2048, 0), (1, 12288, 4096, 0),
+    (8, 1280, 1024, 2), (16, 1280, 1024, 2), (1, 22016, 4096, 2), (12, 2816, 4096, 2),
+])
+def test_w4a16_decode_plan_covers_every_block_once(lib, case):
+    # Host arithmetic of the decode kernel, walked the way the kernel walks it: every (k-block,
+    # 16-column group) of the packed matrix is read by exactly one warp of one CTA, ring slots are
+    # reused only after they were consumed, and the plan fits in shared memory.
+    M, N, K, mode = case
+    pl = _decode_plan(lib, M, N, K, mode)
+    gu = mode == 2
+    kbt = K // 64
+    ncg_max = pl["ncg"]
+    assert ncg_max == 6 if M > 8 else ncg_max in (5, 8)
+    assert pl["gpu"] == (2 if gu else 1)
+    assert pl["units"] == (N // 32 if gu else -(-N // 16))
+    assert pl["grid"] == pl["clusters"] * pl["ksplit"] and pl["grid"] <= 148
+    assert pl["ksplit"] in (1, 2, 4) and pl["upc"] * pl["gpu"] <= ncg_max
+    assert pl["slot_bytes"] == pl["upc"] * pl["gpu"] * 512 and pl["depth"] >= 1
+    assert pl["pitch"] >= pl["upc"] * pl["gpu"] * 16 and pl["pitch"] % 32 in (4, 20)
+    assert pl["smem_bytes"] <= 227 * 1024
+    assert 16 * pl["depth"] * pl["slot_bytes"] + 17 * M * pl["pitch"] * 4 <= pl["smem_bytes"]
+    # a whole block of groups is read past a chunk's last group: it must stay inside the allocation
+    assert 16 * pl["depth"] * pl["slot_bytes"] - pl["slot_bytes"] + ncg_max * 512 <= pl["smem_bytes"]
+    seen = {}
+    n_groups_total = -(-N // 16)
+    for cluster in range(pl["clusters"]):
+        u0 = cluster * pl["units"] // pl["clusters"]
+        u1 = (cluster + 1) * pl["units"] // pl["clusters"]
+        assert u1 > u0
+        n_chunks = -(-(u1 - u0) // pl["upc"])
+        for rank in range(pl["ksplit"]):
+            k0 = rank * kbt // pl["ksplit"]
+            k1 = (rank + 1) * kbt // pl["ksplit"]
+            for warp in range(16):
+                nkb = -(-(k1 - k0 - warp) // 16) if k1 - k0 > warp else 0
+                for it in range(nkb * n_chunks):
+                    ci = it // nkb
+                    kb = k0 + warp + 16 * (it - ci * nkb)
+                    assert k0 <= kb < k1
+                    v0 = u0 + ci * pl["upc"]
+                    nun = min(u1 - v0, pl["upc"])
+                    assert nun >= 1
+                    for j in range(nun * pl["gpu"]):
+                        col = _group_col(gu, v0, j)
+                        assert col % 16 == 0 and col // 16 < -(-N // 128) * 8
+                        key = (kb, col // 16)
+                        assert key not in seen, key
+                        seen[key] = True
+    assert len(seen) == kbt * n_groups_total
+
+
+def test_w4a16_decode_plan_choices(lib):
+    # 11008 columns: 688 groups on 148 CTAs, whole K per CTA, everything requested at once
+    pl = _decode_plan(lib, 1, 11008, 4096)
+    assert (pl["ksplit"], pl["clusters"], pl["upc"], pl["depth"]) == (1, 148, 5, 4)
+    # 4096 columns: 256 groups would leave 148 CTAs with 1 or 2 each; clusters of 4 split K instead
+    pl = _decode_plan(lib, 4, 4096, 11008)
+    assert pl["ksplit"] == 4 and pl["clusters"] == 37 and pl["upc"] == 7
+    # the decode kernel needs no workspace; more rows or an explicit split use the tcgen05 kernel
+    assert lib.wmma_ops_w4a16_workspace_bytes(16, 11008, 4096, 0) == 0
     assert lib.wmma_ops_w4a16_workspace_bytes(17, 11008, 4096, 0) == 0
-    assert lib.wmma_ops_w4a16_workspace_bytes(16, 11008, 4096, 1) == 0
-    # the overlap switch is a plain setter
+    assert lib.wmma_ops_w4a16_workspace_bytes(16, 11008, 4096, 4) > 0
+    out = (ctypes.c_int * 11)()
+    assert lib.wmma_ops_w4a16_decode_plan(17, 128, 64, 0, 148, out) == _lib.ERR_INVALID
+    assert lib.wmma_ops_w4a16_decode_plan(4, 192, 64, 2, 148, out) == _lib.ERR_INVALID
+    # plain setters
     assert lib.wmma_ops_set_w4a16_overlap(1) == 0 and lib.wmma_ops_set_w4a16_overlap(0) == 0

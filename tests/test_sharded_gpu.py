@@ -46,3 +46,28 @@ def test_layer_full_shapes_few_tokens(cuda, world):
         a2, m2 = layers[0](xd)
         torch.cuda.synchronize()
         assert torch.equal(a2, attn) and torch.equal(m2, mlp)
+
+
+@pytest.mark.parametrize("shape", [("o", 512, 4096), ("down", 1408, 4096), ("down_short", 1280, 4096), ("qkv", 4096, 1536),
+                                   ("gate_up", 4096, 2816)])
+def test_shard_shaped_products_at_8192_tokens(cuda, shape):
+    # one rank's products of the 8-way sharded layer at the workload's full token count, each against
+    # the fp32 oracle: K = 512 (O), K = 1408 / 1280 (down: 11 or 10 groups of the 86), and the
+    # column-parallel shards N = 3 x 512 and N = 2 x 1408
+    from oracle import int4
+    name, K, N = shape
+    T = 8192
+    codes, scales = int4.seeded_w4(K, N, 128, seed=61)
+    g = torch.Generator().manual_seed(62)
+    x = torch.randn(T, K, generator=g).to(torch.float16)
+    ref = int4.w4a16_ref(x, codes, scales, 128)
+    q, sc = w.int4_prepack(codes.to(cuda), scales.to(cuda), 128)
+    xd = x.to(cuda)
+    out = w.matmul_w4a16(xd, q, sc, 128)
+    out16 = w.matmul_w4a16(xd, q, sc, 128, out_dtype=torch.float16, alpha=0.25)
+    torch.cuda.synchronize()
+    w.check_status()
+    e32 = og.rel_frobenius(out, ref)
+    e16 = og.rel_frobenius(out16.float(), 0.25 * ref)
+    print(f"{name} [{T} x {K}] @ [{K} x {N}]: fp32 out {e32:.2e}, fp16 out {e16:.2e}")
+    assert e32 < 1e-3 and e16 < 1e-3

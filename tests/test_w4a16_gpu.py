@@ -187,18 +187,43 @@ def test_w4a16_errors(cuda):
         w.matmul_w4a16(A, q, sc, 128, alpha=2.0)
 
 
-# ---- streaming decode kernel (M <= 16, library-chosen plan) --------------------------------------
-# It applies the fp16 group scale to the fp32 sum of a 64-deep block instead of rounding every
-# weight * scale product to fp16 first, so it sits about 2e-4 (relative Frobenius) from the oracle,
-# which dequantises to fp16: inside the 1e-3 bound, but not the 1e-6 of the tcgen05 path.
+# ---- decode kernel (M <= 16, library-chosen plan) ------------------------------------------------
+# It multiplies by the exact integers code - 8 and applies the fp16 group scale to the fp32 sum of a
+# 64-deep block instead of rounding every weight * scale product to fp16 first, so it sits about 2e-4
+# (relative Frobenius) from w4a16_ref, which dequantises to fp16: inside the 1e-3 bound. Against its
+# own definition (int4.w4a16_block_scaled_ref) it is held to OWN_TOL per expansion mode.
 
-@pytest.mark.parametrize("case", [
+DECODE_CASES = [
     (1, 128, 64, 64), (2, 8, 64, 64), (5, 136, 512, 64), (9, 1000, 2048, 128), (16, 256, 512, 128),
     (8, 384, 192, 192), (7, 4096, 11008, 128), (16, 40000, 64, 64), (3, 4096, 4096, 64), (12, 11008, 4096, 128),
-])
+    (1, 22016, 4096, 128), (16, 12288, 4096, 128), (4, 4096, 1408, 128),
+]
+# measured error against the block-scaled definition (5e-7: fp32 summation order plus the cancellation of
+# the high-nibble zero points in the constant-operand chain), with margin
+OWN_TOL = 5e-6
+
+
+@pytest.mark.parametrize("case", DECODE_CASES)
 def test_streaming_decode_shapes(cuda, case):
     M, N, K, group = case
     assert _w4_case(cuda, M, N, K, group, 0, seed=21) < TOL
+
+
+@pytest.mark.parametrize("case", [(1, 11008, 4096, 128), (16, 11008, 4096, 128), (8, 4096, 11008, 128), (5, 136, 512, 64),
+                                  (13, 12288, 4096, 128), (2, 22016, 4096, 128)])
+def test_decode_kernel_against_its_own_definition(cuda, case):
+    M, N, K, group = case
+    codes, scales = int4.seeded_w4(K, N, group, seed=51)
+    A, _ = og.seeded_ab(M, 8, K, seed=52)
+    q, sc = w.int4_prepack(codes.to(cuda), scales.to(cuda), group)
+    C = w.matmul_w4a16(A.to(cuda), q, sc, group)
+    C2 = w.matmul_w4a16(A.to(cuda), q, sc, group)
+    _sync_ok()
+    own = og.rel_frobenius(C, int4.w4a16_block_scaled_ref(A, codes, scales, group))
+    print(f"decode M={M} N={N} K={K}: {own:.2e} vs block-scaled definition, "
+          f"{og.rel_frobenius(C, int4.w4a16_ref(A, codes, scales, group)):.2e} vs fp16-rounded weights")
+    assert own < OWN_TOL
+    assert torch.equal(C, C2)      # fixed summation order
 
 
 @pytest.mark.parametrize("M", [1, 8, 9, 16])
@@ -219,9 +244,8 @@ def test_streaming_decode_output_modes(cuda, M):
     assert og.rel_frobenius(act.float(), 0.25 * torch.nn.functional.silu(ref[:, :F]) * ref[:, F:]) < 2e-3
 
 
-def test_streaming_decode_reuses_one_workspace_across_shapes(cuda):
-    # products with few and with many column tiles share the library's workspace: the arrival
-    # counters sit in a fixed area, so one call's partial sums never land in the next call's counters
+def test_decode_and_split_products_alternate(cuda):
+    # decode products (no workspace) of different plans alternate with each other; results repeat bit for bit
     shapes = [(4, 256, 4096), (16, 11008, 4096), (2, 128, 8192), (16, 11008, 4096), (4, 256, 4096)]
     data = {}
     for (M, N, K) in set(shapes):

@@ -8,6 +8,7 @@ CUDA through libwmma_ops_b200.so; there is no CPU or library fallback.
 from . import _lib
 from .ops import (  # noqa: F401
     check_status,
+    reset_workspaces,
     gemm,
     gemm_adaptive,
     gemm_inplace,

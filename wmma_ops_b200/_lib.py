@@ -10,6 +10,9 @@ from pathlib import Path
 
 _PKG = Path(__file__).resolve().parent
 LIB_PATH = _PKG / "libwmma_ops_b200.so"
+# the same sources built with -DWMMA_OPS_DEBUG_CHECKS: device-side index checks that record a
+# fault in the status word and skip the access (loaded when WMMA_OPS_DEBUG=1)
+DEBUG_LIB_PATH = _PKG / "libwmma_ops_b200_debug.so"
 
 OK = 0
 ERR_INVALID = 1
@@ -44,6 +47,7 @@ SIGNATURES = {
     "wmma_ops_int4_unpack": (_c_int, [_vp, _vp, _c_int, _c_int, _vp]),
     "wmma_ops_int4_dequant": (_c_int, [_vp, _vp, _vp, _c_int, _c_int, _c_int, _vp]),
     "wmma_ops_set_w4a16_overlap": (_c_int, [_c_int]),
+    "wmma_ops_w4a16_decode_plan": (_c_int, [_c_int, _c_int, _c_int, _c_int, _c_int, ctypes.POINTER(_c_int)]),
     "wmma_ops_w4a16_workspace_bytes": (_c_size_t, [_c_int, _c_int, _c_int, _c_int]),
     "wmma_ops_w4a16_select_split": (_c_int, [_c_int, _c_int, _c_int, _c_int]),
     "wmma_ops_w4a16_gemm": (_c_int, [_vp, _vp, _vp, _vp, _c_int, _c_int, _c_int, _c_int, _c_int, _vp,
@@ -53,6 +57,9 @@ SIGNATURES = {
     "wmma_ops_fmha_fwd": (_c_int, [_vp, _vp, _vp, _vp, _c_int, _c_int, _c_int, _c_int, _c_float, _c_int,
                                    _vp, _vp]),
     "wmma_ops_multimem_allreduce_f16": (_c_int, [_vp, _c_size_t, _c_int, _c_int, _c_int, _vp]),
+    "wmma_ops_selftest_wait_expiry": (_c_int, [ctypes.c_longlong, _c_int, _vp, _vp]),
+    "wmma_ops_selftest_debug_index": (_c_int, [_c_int, _c_int, _vp, _vp, _vp]),
+    "wmma_ops_debug_checks_enabled": (_c_int, []),
 }
 
 _lib = None
@@ -63,7 +70,8 @@ def load() -> ctypes.CDLL:
     global _lib
     if _lib is not None:
         return _lib
-    path = Path(os.environ.get("WMMA_OPS_B200_LIB", LIB_PATH))
+    debug = os.environ.get("WMMA_OPS_DEBUG", "0") not in ("", "0")
+    path = Path(os.environ.get("WMMA_OPS_B200_LIB", DEBUG_LIB_PATH if debug else LIB_PATH))
     if not path.exists():
         raise RuntimeError(
             f"{path} not found: the CUDA library is not built. Run `python -m wmma_ops_b200.csrc.build` "

@@ -347,7 +347,7 @@ fmha_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
                 uint32_t v[32];
                 tmem_ld_32x32b_x32(o_addr + c * 32, v);
                 tmem_wait_ld();
-                if (q < p.S) {
+                if (q < p.S && WB_DEBUG_INDEX(q >= 0 && bh >= 0 && bh < p.B * p.H, p.status, 103, q)) {
 #pragma unroll
                     for (int g = 0; g < 4; ++g) {
                         uint4 o;
@@ -373,13 +373,13 @@ fmha_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
 template <int D, int BN>
 static int launch_fmha(const void* Q, const void* K, const void* V, const FaParams& p, cudaStream_t stream) {
     using Cfg = FaCfg<D, BN>;
-    static bool attr_set[64] = {};
+    static std::atomic<bool> attr_set[64];  // per device; setting the attribute twice is harmless
     int dev = 0;
     WB_CHECK_CUDA(cudaGetDevice(&dev));
-    if (dev >= 0 && dev < 64 && !attr_set[dev]) {
+    if (dev >= 0 && dev < 64 && !attr_set[dev].load(std::memory_order_acquire)) {
         WB_CHECK_CUDA(cudaFuncSetAttribute(fmha_fwd_kernel<D, BN>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                            Cfg::SMEM_BYTES));
-        attr_set[dev] = true;
+        attr_set[dev].store(true, std::memory_order_release);
     }
     CUtensorMap tq, tk, tv;
     const uint64_t dims[3] = {static_cast<uint64_t>(D), static_cast<uint64_t>(p.S),

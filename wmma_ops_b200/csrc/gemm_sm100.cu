@@ -234,7 +234,7 @@ gemm_f16f32_kernel(const __grid_constant__ CUtensorMap tmap_a,
 #pragma unroll
                     for (int j = 0; j < 8; ++j) {
                         const int col = col0 + j * 4;
-                        if (col < p.N) {
+                        if (col < p.N && WB_DEBUG_INDEX(row >= 0 && col >= 0 && col + 4 <= p.N, p.status, 100, col)) {
                             float4 v;
                             v.x = alpha * __uint_as_float(r[4 * j + 0]);
                             v.y = alpha * __uint_as_float(r[4 * j + 1]);
@@ -451,7 +451,7 @@ gemm_f16f32_pair_kernel(const __grid_constant__ CUtensorMap tmap_a,
 #pragma unroll
                     for (int j = 0; j < 8; ++j) {
                         const int col = col0 + j * 4;
-                        if (col < p.N) {
+                        if (col < p.N && WB_DEBUG_INDEX(row >= 0 && col >= 0 && col + 4 <= p.N, p.status, 100, col)) {
                             float4 v;
                             v.x = alpha * __uint_as_float(r[4 * j + 0]);
                             v.y = alpha * __uint_as_float(r[4 * j + 1]);
@@ -599,14 +599,14 @@ template <int BN>
 static int launch_gemm(const CUtensorMap& ta, const CUtensorMap& tb, const GemmParams& p, int sms,
                        cudaStream_t stream) {
     using Cfg = GemmCfg<BN>;
-    static bool attr_set[64] = {};
+    static std::atomic<bool> attr_set[64];  // per device; setting the attribute twice is harmless
     int dev = 0;
     WB_CHECK_CUDA(cudaGetDevice(&dev));
-    if (dev >= 0 && dev < 64 && !attr_set[dev]) {
+    if (dev >= 0 && dev < 64 && !attr_set[dev].load(std::memory_order_acquire)) {
         WB_CHECK_CUDA(cudaFuncSetAttribute(gemm_f16f32_kernel<BN>,
                                            cudaFuncAttributeMaxDynamicSharedMemorySize,
                                            Cfg::SMEM_BYTES));
-        attr_set[dev] = true;
+        attr_set[dev].store(true, std::memory_order_release);
     }
     const int units = p.m_blocks * p.n_blocks * p.split_k;
     const int grid = units < sms ? units : sms;
@@ -617,13 +617,13 @@ static int launch_gemm(const CUtensorMap& ta, const CUtensorMap& tb, const GemmP
 
 static int launch_gemm_pair(const CUtensorMap& ta, const CUtensorMap& tb, GemmParams p, int sms,
                             cudaStream_t stream) {
-    static bool attr_set[64] = {};
+    static std::atomic<bool> attr_set[64];  // per device; setting the attribute twice is harmless
     int dev = 0;
     WB_CHECK_CUDA(cudaGetDevice(&dev));
-    if (dev >= 0 && dev < 64 && !attr_set[dev]) {
+    if (dev >= 0 && dev < 64 && !attr_set[dev].load(std::memory_order_acquire)) {
         WB_CHECK_CUDA(cudaFuncSetAttribute(gemm_f16f32_pair_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                            PAIR_SMEM_BYTES));
-        attr_set[dev] = true;
+        attr_set[dev].store(true, std::memory_order_release);
     }
     p.m_blocks = ceil_div(p.M, 256);
     p.n_blocks = ceil_div(p.N, PAIR_BN);
@@ -796,10 +796,14 @@ extern "C" int wmma_ops_gemm_f16f32_splitk_static(const void* A, const void* B, 
     // Resolve the tile and slice count here, so that the size check below sees the final plan.
     if (tile_cfg == WMMA_OPS_TILE_AUTO) {
         int auto_split = 1;
-        select_tile_impl(M, N, K, 148, &tile_cfg, &auto_split);
+        select_tile_impl(M, N, K, sm_count(), &tile_cfg, &auto_split);
         if (split_k == 0) split_k = auto_split;
     }
     if (split_k < 1) split_k = 1;
+    // the clamp wmma_ops_gemm_f16f32 applies: at most one slice per 64-deep k-block, no empty slice
+    const int kb_total = ceil_div(K, BK);
+    if (split_k > kb_total) split_k = kb_total;
+    split_k = ceil_div(kb_total, ceil_div(kb_total, split_k));
     const size_t need = wmma_ops_gemm_workspace_bytes(M, N, K, split_k);
     WB_REQUIRE(need <= STATIC_SCRATCH_BYTES, WMMA_OPS_ERR_WORKSPACE,
                "gemm_splitk_static: split_k=%d of a %d x %d product needs %zu bytes of partial sums, more than "

@@ -15,9 +15,7 @@ void set_error(const char* fmt, ...) {
     va_end(ap);
 }
 
-int g_sm_margin = 0;
-
-int sm_margin() { return g_sm_margin; }
+std::atomic<int> g_sm_margin{0};
 
 int sm_count() {
     static int cached[64];
@@ -32,7 +30,7 @@ int sm_count() {
         cached[dev] = n;
     }
     // SMs left free for other kernels (collectives) that must run beside the persistent ones
-    const int usable = cached[dev] - g_sm_margin;
+    const int usable = cached[dev] - g_sm_margin.load(std::memory_order_relaxed);
     return usable > 8 ? usable : 8;
 }
 
@@ -97,6 +95,6 @@ extern "C" int wmma_ops_set_sm_margin(int sms) {
         wb::set_error("sm margin must be in 0..64 (got %d)", sms);
         return WMMA_OPS_ERR_INVALID;
     }
-    wb::g_sm_margin = sms;
+    wb::g_sm_margin.store(sms, std::memory_order_relaxed);
     return WMMA_OPS_OK;
 }

@@ -3,6 +3,7 @@
 #pragma once
 #include <cuda.h>
 #include <cuda_runtime.h>
+#include <atomic>
 #include <cstdarg>
 #include <cstdint>
 #include <cstdio>
@@ -34,7 +35,7 @@ void set_error(const char* fmt, ...);  // stores a thread-local message for wmma
 // Number of SMs the persistent kernels may occupy on the current device: the device's SM count
 // (cached per device index) minus the margin set with wmma_ops_set_sm_margin.
 int sm_count();
-extern int g_sm_margin;
+extern std::atomic<int> g_sm_margin;  // process-wide switch, read once per launch
 
 // Encodes a tiled tensor map. dims/strides are innermost first; strides[0] is implied
 // (element size) and strides[i>0] are in bytes. Returns 0 or WMMA_OPS_ERR_*.

@@ -101,6 +101,36 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity) {
     return true;
 }
 
+// The same wait with the limit as an argument (SM cycles), checked every 64 polls: for waits whose
+// limit is a launch parameter, such as the self-test kernel that lets a wait run out on purpose.
+__device__ __forceinline__ bool mbar_wait_limit(uint32_t bar, uint32_t parity, long long limit_cycles) {
+    if (mbar_try_wait(bar, parity)) return true;
+    const long long t0 = clock64();
+    uint32_t spins = 0;
+    while (!mbar_try_wait(bar, parity)) {
+        if ((++spins & 0x3f) == 0 && clock64() - t0 > limit_cycles) return false;
+    }
+    return true;
+}
+
+// Debug build (-DWMMA_OPS_DEBUG_CHECKS, the library the Python layer loads when WMMA_OPS_DEBUG=1):
+// WB_DEBUG_INDEX(ok, status, where, detail) evaluates to `ok`; when `ok` is false it records
+// {code 9, where, block, detail} in the launch's status word, and the caller skips the access.
+// In the normal build it evaluates to true and the check disappears. Nothing traps.
+__device__ __forceinline__ bool debug_index_report(bool ok, int* status, int where, int detail) {
+    if (!ok && status != nullptr && atomicCAS(status, 0, 9) == 0) {
+        status[1] = where;
+        status[2] = static_cast<int>(blockIdx.x);
+        status[3] = detail;
+    }
+    return ok;
+}
+#ifdef WMMA_OPS_DEBUG_CHECKS
+#define WB_DEBUG_INDEX(ok, status, where, detail) ::wb::debug_index_report((ok), (status), (where), (detail))
+#else
+#define WB_DEBUG_INDEX(ok, status, where, detail) (true)
+#endif
+
 // Bounded wait for roles that are idle for long stretches (an epilogue warp waiting for a whole
 // tile, a producer waiting for a free slot): sleeps between polls so that it does not take
 // issue slots from the warps doing the work.

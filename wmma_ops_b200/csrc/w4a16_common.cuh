@@ -18,7 +18,7 @@ constexpr int W4_THREADS = 512;
 constexpr int W4_DQ_WARPS = 8;     // each dequant warp expands a whole 4 KB block; 8 blocks in flight
 
 struct W4Params {
-    const __half* X;   // activations [M, K] (read directly by the streaming decode kernel)
+    const __half* X;   // activations [M, K] (read directly by the decode kernel)
     const uint32_t* qweight;
     const __half* scales;
     float* C;          // fp32 output (out_mode 0)
@@ -138,28 +138,29 @@ __device__ __forceinline__ uint32_t dq_pair(uint32_t t, __half2 scale2) {
     return *reinterpret_cast<const uint32_t*>(&r);
 }
 
-// ---------------------------------------------------------------- streaming decode kernel
-// (w4a16_stream_sm100.cu) for products with at most W4_STREAM_MAX_M activation rows.
+// ---------------------------------------------------------------- decode kernel
+// (w4a16_decode_sm100.cu) for products with at most W4_STREAM_MAX_M activation rows.
 constexpr int W4_STREAM_MAX_M = 16;
 
-// Bytes at the start of a workspace that hold the per-tile arrival counters. The area has a fixed
-// size for every product with up to 16384 tiles, so that a caller who reuses one zero-initialised
-// buffer for products of different shapes never gets one call's partial sums into the counters of
-// the next (the kernels leave the counters at zero).
+// Bytes at the start of a workspace that hold the per-tile arrival counters of the tcgen05 kernel's
+// partial-sum plans. The area has a fixed size for every product with up to 16384 tiles, so that a
+// caller who reuses one zero-initialised buffer for products of different shapes never gets one
+// call's partial sums into the counters of the next (the kernels leave the counters at zero).
 inline size_t w4_counter_bytes(int tiles) {
     const size_t need = (static_cast<size_t>(tiles) * 4 + 255) / 256 * 256;
     return need < 65536 ? 65536 : need;
 }
 
-struct W4StreamPlan {
-    int n_tiles, kb_total, grid, max_slices;
-    size_t workspace_bytes() const {
-        return w4_counter_bytes(n_tiles) + static_cast<size_t>(n_tiles) * max_slices * W4_STREAM_MAX_M * W4_TILE_N * sizeof(float);
-    }
+// How the decode kernel cuts a product up (host arithmetic, no GPU needed). Units are groups of 16
+// columns (pairs of a gate and an up group in the fused gate/up mode); cluster c of `clusters` owns
+// the units [c*units/clusters, (c+1)*units/clusters) and walks them in chunks of `upc`; the `ksplit`
+// CTAs of a cluster each take one part of K. The decode kernel needs no workspace.
+struct W4DecodePlan {
+    int kb_total, n_tiles, gpu, units, ksplit, clusters, upc, ncg, slot_bytes, pitch, depth;
+    int red_off, out_off, bar_off, smem_bytes, grid;
 };
 
-W4StreamPlan w4_stream_plan(int N, int K, int sms);
-// p.n_tiles, p.kb_total, p.max_slices, p.counters and p.partials must follow the plan.
-int w4_stream_launch(const W4Params& p, int grid, cudaStream_t stream);
+W4DecodePlan w4_decode_plan(int M, int N, int K, int out_mode, int sms);
+int w4_decode_launch(const W4Params& p, const W4DecodePlan& d, cudaStream_t stream);
 
 }  // namespace wb

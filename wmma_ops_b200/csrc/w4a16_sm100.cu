@@ -354,7 +354,7 @@ w4a16_gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_const
 #pragma unroll
                         for (int j = 0; j < CH; ++j) {
                             const int t = t0 + c * CH + j;
-                            if (t < p.M) p.C[static_cast<size_t>(t) * p.N + n] = __uint_as_float(v[j]);
+                            if (t < p.M && WB_DEBUG_INDEX(t >= 0 && n >= 0, p.status, 101, n)) p.C[static_cast<size_t>(t) * p.N + n] = __uint_as_float(v[j]);
                         }
                     }
                 } else if (p.out_mode == 1) {
@@ -362,7 +362,7 @@ w4a16_gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_const
 #pragma unroll
                         for (int j = 0; j < CH; ++j) {
                             const int t = t0 + c * CH + j;
-                            if (t < p.M)
+                            if (t < p.M && WB_DEBUG_INDEX(t >= 0 && n >= 0, p.status, 102, n))
                                 p.C16[static_cast<size_t>(t) * p.N + n] = __float2half_rn(p.alpha * __uint_as_float(v[j]));
                         }
                     }
@@ -579,13 +579,13 @@ template <int BT, bool WM>
 static int launch_w4(const CUtensorMap& tx, const CUtensorMap& tw, const CUtensorMap& tsc, const W4Params& p,
                      int grid, cudaStream_t stream) {
     using Cfg = W4Cfg<BT, WM>;
-    static bool attr_set[64] = {};
+    static std::atomic<bool> attr_set[64];  // per device; setting the attribute twice is harmless
     int dev = 0;
     WB_CHECK_CUDA(cudaGetDevice(&dev));
-    if (dev >= 0 && dev < 64 && !attr_set[dev]) {
+    if (dev >= 0 && dev < 64 && !attr_set[dev].load(std::memory_order_acquire)) {
         WB_CHECK_CUDA(cudaFuncSetAttribute(w4a16_gemm_kernel<BT, WM>,
                                            cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM_BYTES));
-        attr_set[dev] = true;
+        attr_set[dev].store(true, std::memory_order_release);
     }
     w4a16_gemm_kernel<BT, WM><<<grid, W4_THREADS, Cfg::SMEM_BYTES, stream>>>(tx, tw, tsc, p);
     WB_CHECK_CUDA(cudaGetLastError());
@@ -648,7 +648,7 @@ extern "C" int wmma_ops_w4a16_select_split(int M, int N, int K, int num_sms) {
 
 extern "C" size_t wmma_ops_w4a16_workspace_bytes(int M, int N, int K, int split_k) {
     if (M < 1 || N < 8 || K < 64 || K % 64 != 0) return 0;
-    if (wb::w4_use_stream(M, N, K, split_k)) return wb::w4_stream_plan(N, K, wb::sm_count()).workspace_bytes();
+    if (wb::w4_use_stream(M, N, K, split_k)) return 0;  // the decode kernel keeps its sums on chip
     return wb::w4_make_plan(M, N, K, split_k, wb::sm_count()).workspace_bytes();
 }
 
@@ -712,24 +712,15 @@ extern "C" int wmma_ops_w4a16_gemm_ex(const void* A, const void* qweight, const 
     p.partials = nullptr;
     p.counters = nullptr;
     if (w4_use_stream(M, N, K, split_k)) {
-        // decode: one pass over the packed weights, all SMs streaming equal shares
-        const W4StreamPlan sp = w4_stream_plan(N, K, sms);
-        p.n_tiles = sp.n_tiles;
+        // decode: one pass over the packed weights, every CTA owning a range of columns
+        const W4DecodePlan dp = w4_decode_plan(M, N, K, out_mode, sms);
+        p.n_tiles = dp.n_tiles;
         p.t_tiles = 1;
-        p.kb_total = sp.kb_total;
+        p.kb_total = dp.kb_total;
         p.split = 1;
         p.balanced = 0;
-        p.max_slices = sp.max_slices;
-        const size_t need = sp.workspace_bytes();
-        WB_REQUIRE(workspace != nullptr && workspace_bytes >= need, WMMA_OPS_ERR_WORKSPACE,
-                   "w4a16: a product with M <= %d needs %zu bytes of zero-initialised workspace (got %zu); see "
-                   "wmma_ops_w4a16_workspace_bytes",
-                   W4_STREAM_MAX_M, need, workspace_bytes);
-        WB_REQUIRE(reinterpret_cast<uintptr_t>(workspace) % 16 == 0, WMMA_OPS_ERR_INVALID,
-                   "workspace must be 16-byte aligned");
-        p.counters = static_cast<int*>(workspace);
-        p.partials = reinterpret_cast<float*>(static_cast<uint8_t*>(workspace) + w4_counter_bytes(p.n_tiles));
-        return w4_stream_launch(p, sp.grid, stream);
+        p.max_slices = 1;
+        return w4_decode_launch(p, dp, stream);
     }
     WB_REQUIRE(out_mode == WMMA_OPS_W4_OUT_F32 || !plan.partials(), WMMA_OPS_ERR_INVALID,
                "w4a16: fp16 / fused outputs need a plan without partial sums (pass split_k = 1)");

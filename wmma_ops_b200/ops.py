@@ -29,7 +29,11 @@ def _status_word(device: torch.device) -> torch.Tensor:
 
 
 def check_status(device=None) -> None:
-    """Synchronises `device` and raises if a kernel's bounded wait gave up since the last check."""
+    """Synchronises `device` and raises if a kernel's bounded wait gave up since the last check.
+
+    A kernel that gives up may leave arrival counters of the zero-initialised W4A16 workspaces
+    non-zero (only the last CTA to arrive resets them), so those workspaces of the device are
+    cleared together with the status word before the error is raised."""
     device = torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)
     if device.index is None:
         device = torch.device("cuda", torch.cuda.current_device())
@@ -37,20 +41,44 @@ def check_status(device=None) -> None:
     vals = t.cpu().tolist()
     if vals[0] != 0:
         t.zero_()
+        reset_workspaces(device)
         raise RuntimeError(
             f"wmma_ops_b200 kernel gave up waiting: code={vals[0]} role={vals[1]} block={vals[2]} detail={vals[3]}"
         )
 
 
+def reset_workspaces(device) -> None:
+    """Zero-fills every zero-initialised scratch buffer this module holds for `device` (W4A16
+    partial sums and their arrival counters). Called after a non-zero status word."""
+    device = torch.device(device)
+    for (dtype, index, _stream_id, zero_init), bufs in _workspaces.items():
+        if zero_init and dtype == device.type and index == device.index:
+            for b in bufs:
+                b.zero_()
+
+
 def _workspace(device: torch.device, nbytes: int, zero_init: bool = False) -> torch.Tensor:
-    """Per-device scratch buffer that only grows (split-K partials, arrival counters)."""
-    key = (device.type, device.index, zero_init)
-    t = _workspaces.get(key)
-    if t is None or t.numel() < nbytes:
-        size = max(nbytes, 1 << 20)
-        t = torch.zeros(size, dtype=torch.uint8, device=device) if zero_init else torch.empty(
-            size, dtype=torch.uint8, device=device)
-        _workspaces[key] = t
+    """Scratch buffer (split-K partials; W4A16 partials and arrival counters) for the current
+    stream of `device`.
+
+    One buffer per (device, stream): kernels on different streams may overlap on the GPU and must
+    not share partial sums or arrival counters; calls on one stream are ordered and may. A buffer
+    that has been handed out is never freed (a kernel still running, or a captured CUDA graph, may
+    hold its address): when a larger one is needed the old one is kept in the list. While the stream
+    is being captured the buffer cannot grow; make the first call of each shape before capture."""
+    stream_id = torch.cuda.current_stream(device).cuda_stream
+    key = (device.type, device.index, stream_id, zero_init)
+    bufs = _workspaces.setdefault(key, [])
+    if bufs and bufs[-1].numel() >= nbytes:
+        return bufs[-1]
+    if torch.cuda.is_current_stream_capturing():
+        raise RuntimeError(
+            f"wmma_ops_b200: this call needs {nbytes} bytes of scratch but the stream is being captured and its "
+            "scratch buffer cannot grow now; run the same call once before the capture")
+    size = max(nbytes, 1 << 20)
+    t = torch.zeros(size, dtype=torch.uint8, device=device) if zero_init else torch.empty(
+        size, dtype=torch.uint8, device=device)
+    bufs.append(t)
     return t
 
 
@@ -93,12 +121,15 @@ def _require(cond: bool, msg: str) -> None:
 
 
 # --------------------------------------------------------------------------- validation
-def _check_ab(A, B, where: str = "CUDA", same_device: bool = True) -> Tuple[torch.Tensor, torch.Tensor, int, int, int]:
-    """The reference's TORCH_CHECK sequence (wmma_gemm.hip:1433-1446), same order and text."""
+def _check_ab(A, B, where: str = "CUDA") -> Tuple[torch.Tensor, torch.Tensor, int, int, int]:
+    """The reference's TORCH_CHECK sequence (wmma_gemm.hip:1433-1446), same order and text.
+
+    The device check is made for every entry point. The reference omits it in matmul_tiled and some
+    variants (wmma_gemm.hip:1473-1480), where operands on two GPUs reach the kernel; here that would
+    put another GPU's memory behind a TMA tensor map, so it is an error everywhere."""
     _require(isinstance(A, torch.Tensor) and isinstance(B, torch.Tensor), "Inputs must be tensors")
     _require(A.is_cuda and B.is_cuda, f"Inputs must be {where} tensors")
-    if same_device:
-        _require(A.device == B.device, "Inputs must be on same device")
+    _require(A.device == B.device, "Inputs must be on same device")
     _require(A.dtype == torch.float16 and B.dtype == torch.float16, "Inputs must be float16")
     _require(A.dim() == 2 and B.dim() == 2, "Inputs must be 2D")
     _require(A.size(1) == B.size(0), "Inner dimensions must match")
@@ -170,9 +201,8 @@ def select_tile(M: int, N: int, K: int, num_sms: int = 148) -> Tuple[int, int]:
     return cfg.value, sk.value
 
 
-def _matmul_impl(A, B, tile_cfg: int, split_k: int, where: str = "CUDA", same_device: bool = True,
-                 extra=None) -> torch.Tensor:
-    A, B, M, N, K = _check_ab(A, B, where, same_device)
+def _matmul_impl(A, B, tile_cfg: int, split_k: int, where: str = "CUDA", extra=None) -> torch.Tensor:
+    A, B, M, N, K = _check_ab(A, B, where)
     if extra is not None:
         extra(M, N, K)
     A, B = _finish_ab(A, B)
@@ -213,7 +243,7 @@ def matmul_tiled(A: torch.Tensor, B: torch.Tensor, tile_config: int) -> torch.Te
     """C = A @ B with an explicit tile shape (wmma_matmul_tiled, wmma_gemm.hip:1473-1528).
     The reference's 0..3 (64x64, 128x64, 256x64, 128x128) select the four Blackwell tiles
     128x64, 128x128, 128x256 and the 256x256 CTA pair; other values raise the reference's error."""
-    A, B, M, N, K = _check_ab(A, B, "CUDA", same_device=False)
+    A, B, M, N, K = _check_ab(A, B, "CUDA")
     A, B = _finish_ab(A, B)
     if tile_config not in _TILED_MAP:
         raise RuntimeError("Invalid tile_config: 0=64x64, 1=128x64, 2=256x64, 3=128x128")
@@ -267,14 +297,14 @@ def matmul_kunroll(A, B):
     """Alias with wmma_matmul_kunroll's K % 32 check (wmma_gemm.hip:1606-1622)."""
     def extra(M, N, K):
         _require(K % 32 == 0, "K dimension must be a multiple of 32 for K-unrolled kernel")
-    return _matmul_impl(A, B, _DEFAULT_TILE, 1, same_device=False, extra=extra)
+    return _matmul_impl(A, B, _DEFAULT_TILE, 1, extra=extra)
 
 
 def matmul_quad(A, B):
     """Alias with wmma_matmul_quad's K % 16 check (wmma_gemm.hip:1648-1664)."""
     def extra(M, N, K):
         _require(K % 16 == 0, "K dimension must be a multiple of 16 for quad-buffered kernel")
-    return _matmul_impl(A, B, _DEFAULT_TILE, 1, same_device=False, extra=extra)
+    return _matmul_impl(A, B, _DEFAULT_TILE, 1, extra=extra)
 
 
 def matmul_native(A, B):
@@ -289,27 +319,27 @@ def matmul_zerocopy(A, B):
 
 def matmul_highOcc(A, B):
     """Alias on the narrowest tile (wmma_matmul_highOcc, wmma_gemm.hip:1688-1724, is the reference's small-tile variant)."""
-    return _matmul_impl(A, B, _lib.TILE_128x64, 1, same_device=False)
+    return _matmul_impl(A, B, _lib.TILE_128x64, 1)
 
 
 def matmul_noPrefetch(A, B):
     """Alias (wmma_matmul_noPrefetch, wmma_gemm.hip:1727-1765)."""
-    return _matmul_impl(A, B, _DEFAULT_TILE, 1, same_device=False)
+    return _matmul_impl(A, B, _DEFAULT_TILE, 1)
 
 
 def matmul_asmOpt(A, B):
     """Alias (wmma_matmul_asmOpt, wmma_gemm.hip:1768-1804)."""
-    return _matmul_impl(A, B, _DEFAULT_TILE, 1, same_device=False)
+    return _matmul_impl(A, B, _DEFAULT_TILE, 1)
 
 
 def matmul_swizzled(A, B):
     """Alias (wmma_matmul_swizzled, wmma_gemm.hip:1807-1842); the 128-byte hardware swizzle is always on."""
-    return _matmul_impl(A, B, _DEFAULT_TILE, 1, same_device=False)
+    return _matmul_impl(A, B, _DEFAULT_TILE, 1)
 
 
 def matmul_xor_optimized(A, B):
     """Alias (wmma_matmul_xor_optimized, wmma_gemm.hip:1845-1888)."""
-    return _matmul_impl(A, B, _DEFAULT_TILE, 1, same_device=False)
+    return _matmul_impl(A, B, _DEFAULT_TILE, 1)
 
 
 def matmul_coop(A, B):

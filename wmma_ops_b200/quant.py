@@ -104,8 +104,10 @@ def matmul_w4a16(A: torch.Tensor, qweight: torch.Tensor, scales: torch.Tensor, g
                  split_k: int = 0, out_dtype: torch.dtype = torch.float32, alpha: float = 1.0,
                  epilogue: str = "none", out: Optional[torch.Tensor] = None) -> torch.Tensor:
     """C [M,N] = A fp16 [M,K] @ dequant(qweight, scales); the weights are expanded inside the kernel,
-    never written to memory. split_k=0 lets the library choose: up to 16 rows go to the streaming
-    decode kernel (all SMs stream equal shares of the packed weights), more rows to the tcgen05 kernel.
+    never written to memory. split_k=0 lets the library choose: up to 16 rows go to the decode
+    kernel (every CTA owns a range of columns and streams their packed weights over all of K; exact
+    integer weights, the group scale applied to fp32 block sums), more rows to the tcgen05 kernel
+    (weights rounded to fp16 as int4_dequant does).
 
     out_dtype=torch.float32 (default) returns the fp32 accumulators. out_dtype=torch.float16 returns
     half(alpha * acc). epilogue="silu_mul" (weights prepared with interleave_gate_up) returns
