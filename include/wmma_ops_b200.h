@@ -58,6 +58,14 @@ int wmma_ops_set_sm_margin(int sms);
  * split_k::compute_config (wmma_xor_swizzle.hpp:293-332). Pure host arithmetic. */
 int wmma_ops_select_tile(int M, int N, int K, int num_sms, int* tile_cfg, int* split_k);
 
+/* Installs a measured tile table (process-wide; n_rows = 0 removes it). rows is n_rows x 6 ints
+ * {M, N, K, num_sms, tile_cfg, split_k}: wmma_ops_select_tile, and every AUTO launch, then return
+ * tile_cfg / split_k for any product in the same shape bucket (ceil(M/128), ceil(N/64), ceil(K/64))
+ * on a device with num_sms SMs, and fall back to the built-in cost model otherwise. The table is
+ * what the tuner (wmma_ops_b200/tune.py) measures and stores; it takes the place of the reference's
+ * generated select_tuned_tile (autotune.py:131-283). */
+int wmma_ops_set_tile_table(const int* rows, int n_rows);
+
 /* Bytes of scratch wmma_ops_gemm_f16f32 needs for this split_k (0 when split_k <= 1):
  * split_k fp32 partial products of M x N, the layout of the reference's split-K
  * workspace (wmma_xor_swizzle.hpp:1196-1210). */
@@ -119,18 +127,21 @@ int wmma_ops_int4_dequant(const void* qweight, const void* scales, void* W_f16, 
 
 /* Overlapped decode launches (off by default; process-wide). When on, the decode kernel
  * (M <= 16, split_k = 0) is launched as a programmatic dependent launch: its CTAs may start, and
- * request their packed-weight segments, while the previous kernel of the stream is still
- * finishing; they wait for that kernel to complete before they read the activations or the
- * scales or touch the output. The caller promises that qweight is not written by the kernels
- * queued just before the call (weights are static in decode). No counterpart in the reference. */
+ * load their scales and request their packed-weight segments, while the previous kernel of the
+ * stream is still finishing; they wait for that kernel to complete before they read the
+ * activations or touch the output. The caller promises that neither qweight nor scales is written
+ * by the kernels queued just before the call (weights are static in decode). No counterpart in the
+ * reference. */
 int wmma_ops_set_w4a16_overlap(int enable);
 
 /* The decode kernel's launch plan for an M x N x K product (M <= 16), host arithmetic only:
- * plan[0..10] = {grid, clusters, ksplit, units, groups_per_unit, units_per_chunk, ring_depth,
- * slot_bytes, reduction_pitch, shared_memory_bytes, groups_per_chunk_of_the_kernel_variant}. Columns are dealt in units of 16 (pairs of a
- * gate and an up group with WMMA_OPS_W4_OUT_F16_SILU_MUL) to `clusters` clusters of `ksplit` CTAs;
- * the CTAs of a cluster split K. num_sms <= 0: 148. No counterpart in the reference. */
-int wmma_ops_w4a16_decode_plan(int M, int N, int K, int out_mode, int num_sms, int* plan);
+ * plan[0..13] = {grid, clusters, ksplit, units, groups_per_unit, units_per_chunk, ring_depth,
+ * slot_bytes, reduction_pitch, shared_memory_bytes, groups_per_chunk_of_the_kernel_variant,
+ * reduction_tiles_over_the_ring, k_blocks_per_segment, staged_row_pitch}. Columns are dealt in
+ * units of 16 (pairs of a gate and an up group with WMMA_OPS_W4_OUT_F16_SILU_MUL) to `clusters`
+ * clusters of `ksplit` CTAs; the CTAs of a cluster split K; activations and scales are staged in
+ * shared memory one segment of K at a time. num_sms <= 0: 148. No counterpart in the reference. */
+int wmma_ops_w4a16_decode_plan(int M, int N, int K, int group_size, int out_mode, int num_sms, int* plan);
 
 /* Bytes of scratch wmma_ops_w4a16_gemm needs for this shape and split_k (partial sums + arrival
  * counters of the tcgen05 kernel's split plans); 0 when the plan has no partial sums, which includes
@@ -191,6 +202,33 @@ int wmma_ops_multimem_allreduce_f16(void* multicast_ptr, size_t n_halves, int ra
  * scale < 0 means 1/sqrt(D). Requirements: D == 128 or D == 64, S >= 1. */
 int wmma_ops_fmha_fwd(const void* Q, const void* K, const void* V, void* O, int B, int H, int S,
                       int D, float scale, int causal, int* status, void* stream);
+
+/* On-disk container for prepacked INT4 weights (written and read by wmma_ops_b200/w4file.py; no
+ * counterpart in the reference, which has no INT4 code). Little endian; every payload starts on a
+ * 256-byte boundary, so a file mapped at a page boundary can be copied to the device block by
+ * block. A file is: one header, n_entries entries, then the payloads.
+ *   qweight payload  uint32 [K/64][ceil(N/128)][128][8], the device layout of wmma_ops_int4_prepack
+ *   scales payload   fp16 [K/group_size][N]
+ * A reader must refuse a version it does not know: the packed block layout is part of the version.
+ * Checksums are CRC-32 (IEEE 802.3, as zlib computes it). */
+#define WMMA_OPS_W4_FILE_MAGIC "W4B200\0\0"
+#define WMMA_OPS_W4_FILE_VERSION 1u
+typedef struct wmma_ops_w4_file_header {
+    char magic[8];          /* WMMA_OPS_W4_FILE_MAGIC */
+    uint32_t version;       /* WMMA_OPS_W4_FILE_VERSION */
+    uint32_t header_bytes;  /* 64 */
+    uint32_t entry_bytes;   /* 128 */
+    uint32_t n_entries;
+    uint32_t table_crc32;   /* of the n_entries entries that follow the header */
+    uint8_t reserved[36];
+} wmma_ops_w4_file_header;
+typedef struct wmma_ops_w4_file_entry {
+    char name[64];          /* UTF-8, zero padded */
+    uint32_t K, N, group_size, zero_point; /* zero_point is 8 */
+    uint64_t qweight_offset, qweight_bytes, scales_offset, scales_bytes; /* offsets from the start of the file */
+    uint32_t qweight_crc32, scales_crc32;
+    uint8_t reserved[8];
+} wmma_ops_w4_file_entry;
 
 /* Self-tests of the failure reporting (no counterpart in the reference, whose kernels have no
  * bounded waits). wmma_ops_selftest_wait_expiry launches one tiny kernel whose only wait is on a

@@ -87,10 +87,11 @@ def test_gemm_argument_checks_need_no_gpu(lib):
     assert lib.wmma_ops_gemm_f16f32(None, None, None, None, 0, 8, 8, 1.0, 0.0, 0, 1, None, 0, None, None) == 0
 
 
-def _decode_plan(lib, M, N, K, mode=0, sms=148):
-    out = (ctypes.c_int * 11)()
-    assert lib.wmma_ops_w4a16_decode_plan(M, N, K, mode, sms, out) == 0, _lib.last_error()
-    keys = ("grid", "clusters", "ksplit", "units", "gpu", "upc", "depth", "slot_bytes", "pitch", "smem_bytes", "ncg")
+def _decode_plan(lib, M, N, K, mode=0, sms=148, group=128):
+    out = (ctypes.c_int * 14)()
+    assert lib.wmma_ops_w4a16_decode_plan(M, N, K, group, mode, sms, out) == 0, _lib.last_error()
+    keys = ("grid", "clusters", "ksplit", "units", "gpu", "upc", "depth", "slot_bytes", "pitch", "smem_bytes", "ncg", "alias_red",
+            "seg_kb", "x_pitch")
     return dict(zip(keys, list(out)))
 
 
@@ -104,7 +105,7 @@ def _group_col(gu, v0, j):
 
 @pytest.mark.parametrize("case", [
     (1, 11008, 4096, 0), (16, 11008, 4096, 0), (8, 4096, 11008, 0), (16, 4096, 4096, 0), (3, 22016, 4096, 0),
-    (16, 128, 64, 0), (2, 8, 64, 0), (5, 136, 512, 0), (16, 40000, 64, 0), (9, 1000, 2048, 0), (1, 12288, 4096, 0),
+    (16, 128, 64, 0), (2, 8, 64, 0), (5, 136, 512, 0), (16, 11008, 11008, 0), (8, 256, 16384, 0), (16, 40000, 64, 0), (9, 1000, 2048, 0), (1, 12288, 4096, 0),
     (8, 1280, 1024, 2), (16, 1280, 1024, 2), (1, 22016, 4096, 2), (12, 2816, 4096, 2),
 ])
 def test_w4a16_decode_plan_covers_every_block_once(lib, case):
@@ -112,7 +113,8 @@ def test_w4a16_decode_plan_covers_every_block_once(lib, case):
     # 16-column group) of the packed matrix is read by exactly one warp of one CTA, ring slots are
     # reused only after they were consumed, and the plan fits in shared memory.
     M, N, K, mode = case
-    pl = _decode_plan(lib, M, N, K, mode)
+    group = 128 if K % 128 == 0 else 64
+    pl = _decode_plan(lib, M, N, K, mode, group=group)
     gu = mode == 2
     kbt = K // 64
     ncg_max = pl["ncg"]
@@ -121,10 +123,16 @@ def test_w4a16_decode_plan_covers_every_block_once(lib, case):
     assert pl["units"] == (N // 32 if gu else -(-N // 16))
     assert pl["grid"] == pl["clusters"] * pl["ksplit"] and pl["grid"] <= 148
     assert pl["ksplit"] in (1, 2, 4) and pl["upc"] * pl["gpu"] <= ncg_max
-    assert pl["slot_bytes"] == pl["upc"] * pl["gpu"] * 512 and pl["depth"] >= 1
+    groups = pl["upc"] * pl["gpu"]
+    assert pl["slot_bytes"] == groups * 512 and pl["depth"] >= 1
+    # activations and scales are staged one K segment at a time: whole rounds of the 16 warps and whole
+    # scale groups, rows 16 bytes longer than their data
+    assert pl["seg_kb"] % 16 == 0 and pl["seg_kb"] % (group // 64) == 0 and pl["x_pitch"] == pl["seg_kb"] * 128 + 16
     assert pl["pitch"] >= pl["upc"] * pl["gpu"] * 16 and pl["pitch"] % 32 in (4, 20)
     assert pl["smem_bytes"] <= 227 * 1024
-    assert 16 * pl["depth"] * pl["slot_bytes"] + 17 * M * pl["pitch"] * 4 <= pl["smem_bytes"]
+    ring, tiles = 16 * pl["depth"] * pl["slot_bytes"], 16 * M * pl["pitch"] * 4
+    staged = M * pl["x_pitch"] + -(-pl["seg_kb"] // (group // 64)) * groups * 32
+    assert (max(ring, tiles) if pl["alias_red"] else ring + tiles) + staged + M * pl["pitch"] * 4 <= pl["smem_bytes"]
     # a whole block of groups is read past a chunk's last group: it must stay inside the allocation
     assert 16 * pl["depth"] * pl["slot_bytes"] - pl["slot_bytes"] + ncg_max * 512 <= pl["smem_bytes"]
     seen = {}
@@ -158,7 +166,13 @@ def test_w4a16_decode_plan_covers_every_block_once(lib, case):
 def test_w4a16_decode_plan_choices(lib):
     # 11008 columns: 688 groups on 148 CTAs, whole K per CTA, everything requested at once
     pl = _decode_plan(lib, 1, 11008, 4096)
-    assert (pl["ksplit"], pl["clusters"], pl["upc"], pl["depth"]) == (1, 148, 5, 4)
+    assert (pl["ksplit"], pl["clusters"], pl["upc"], pl["depth"], pl["alias_red"], pl["seg_kb"]) == (1, 148, 5, 4, 0, 64)
+    # 16 rows: all of X (128 KB) beside the ring would leave one slot per warp, so K is staged in two halves
+    pl = _decode_plan(lib, 16, 11008, 4096)
+    assert pl["depth"] >= 2 and pl["alias_red"] == 1
+    # a long K with 16 rows does not fit at once: it is staged in segments
+    pl = _decode_plan(lib, 16, 11008, 11008)
+    assert pl["seg_kb"] < 172 and pl["depth"] >= 2
     # 4096 columns: 256 groups would leave 148 CTAs with 1 or 2 each; clusters of 4 split K instead
     pl = _decode_plan(lib, 4, 4096, 11008)
     assert pl["ksplit"] == 4 and pl["clusters"] == 37 and pl["upc"] == 7
@@ -166,8 +180,9 @@ def test_w4a16_decode_plan_choices(lib):
     assert lib.wmma_ops_w4a16_workspace_bytes(16, 11008, 4096, 0) == 0
     assert lib.wmma_ops_w4a16_workspace_bytes(17, 11008, 4096, 0) == 0
     assert lib.wmma_ops_w4a16_workspace_bytes(16, 11008, 4096, 4) > 0
-    out = (ctypes.c_int * 11)()
-    assert lib.wmma_ops_w4a16_decode_plan(17, 128, 64, 0, 148, out) == _lib.ERR_INVALID
-    assert lib.wmma_ops_w4a16_decode_plan(4, 192, 64, 2, 148, out) == _lib.ERR_INVALID
+    out = (ctypes.c_int * 14)()
+    assert lib.wmma_ops_w4a16_decode_plan(17, 128, 64, 64, 0, 148, out) == _lib.ERR_INVALID
+    assert lib.wmma_ops_w4a16_decode_plan(4, 192, 64, 64, 2, 148, out) == _lib.ERR_INVALID
+    assert lib.wmma_ops_w4a16_decode_plan(4, 128, 256, 96, 0, 148, out) == _lib.ERR_INVALID
     # plain setters
     assert lib.wmma_ops_set_w4a16_overlap(1) == 0 and lib.wmma_ops_set_w4a16_overlap(0) == 0

@@ -292,3 +292,27 @@ def test_streaming_decode_overlapped_launches(cuda):
         assert og.rel_frobenius(first, int4.w4a16_ref(x0.cpu(), codes, scales, 128)) < TOL
     finally:
         w.set_w4a16_overlap(False)
+
+
+def test_prepacked_weights_survive_the_file_format(cuda, tmp_path):
+    # pack on the device, write the container, load it back onto the device: same bits, same products
+    shapes = {"o": (512, 264, 128), "down": (1408, 4096, 128)}
+    tensors, inputs = {}, {}
+    for name, (K, N, group) in shapes.items():
+        codes, scales = int4.seeded_w4(K, N, group, seed=71)
+        q, sc = w.int4_prepack(codes.to(cuda), scales.to(cuda), group)
+        tensors[name] = (q, sc, group)
+        inputs[name] = (og.seeded_ab(40, 8, K, seed=72)[0].to(cuda), int4.pack_ref(codes))
+    path = tmp_path / "weights.w4"
+    w.save_w4(path, tensors)
+    back = w.load_w4(path)
+    for name, (q, sc, group) in tensors.items():
+        q2, sc2, g2 = back[name]
+        assert q2.is_cuda and g2 == group and torch.equal(q2, q) and torch.equal(sc2, sc)
+        assert torch.equal(q2.cpu(), inputs[name][1])          # the file holds the oracle's packed form
+        x = inputs[name][0]
+        for M in (3, 40):
+            a = w.matmul_w4a16(x[:M].contiguous(), q, sc, group)
+            b = w.matmul_w4a16(x[:M].contiguous(), q2, sc2, g2)
+            _sync_ok()
+            assert torch.equal(a, b)

@@ -37,6 +37,7 @@ SIGNATURES = {
     "wmma_ops_version": (_c_int, []),
     "wmma_ops_set_sm_margin": (_c_int, [_c_int]),
     "wmma_ops_select_tile": (_c_int, [_c_int, _c_int, _c_int, _c_int, ctypes.POINTER(_c_int), ctypes.POINTER(_c_int)]),
+    "wmma_ops_set_tile_table": (_c_int, [ctypes.POINTER(_c_int), _c_int]),
     "wmma_ops_gemm_workspace_bytes": (_c_size_t, [_c_int, _c_int, _c_int, _c_int]),
     "wmma_ops_gemm_f16f32": (_c_int, [_vp, _vp, _vp, _vp, _c_int, _c_int, _c_int, _c_float, _c_float,
                                       _c_int, _c_int, _vp, _c_size_t, _vp, _vp]),
@@ -47,7 +48,7 @@ SIGNATURES = {
     "wmma_ops_int4_unpack": (_c_int, [_vp, _vp, _c_int, _c_int, _vp]),
     "wmma_ops_int4_dequant": (_c_int, [_vp, _vp, _vp, _c_int, _c_int, _c_int, _vp]),
     "wmma_ops_set_w4a16_overlap": (_c_int, [_c_int]),
-    "wmma_ops_w4a16_decode_plan": (_c_int, [_c_int, _c_int, _c_int, _c_int, _c_int, ctypes.POINTER(_c_int)]),
+    "wmma_ops_w4a16_decode_plan": (_c_int, [_c_int, _c_int, _c_int, _c_int, _c_int, _c_int, ctypes.POINTER(_c_int)]),
     "wmma_ops_w4a16_workspace_bytes": (_c_size_t, [_c_int, _c_int, _c_int, _c_int]),
     "wmma_ops_w4a16_select_split": (_c_int, [_c_int, _c_int, _c_int, _c_int]),
     "wmma_ops_w4a16_gemm": (_c_int, [_vp, _vp, _vp, _vp, _c_int, _c_int, _c_int, _c_int, _c_int, _vp,

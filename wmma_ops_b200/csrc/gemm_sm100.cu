@@ -17,6 +17,7 @@
 // warps 2..5 = epilogue (TMEM -> registers -> alpha*acc + beta*C_in -> global).
 // Two TMEM accumulators let the epilogue of one tile overlap the main loop of the next.
 #include <mutex>
+#include <vector>
 
 #include "host_common.cuh"
 #include "ptx.cuh"
@@ -545,7 +546,31 @@ static double kblock_cost(int bn) {
 }
 constexpr double PAIR_KBLOCK_COST = 610.0;  // per pair of SMs, 256x256x64
 
+// Measured tile table (wmma_ops_set_tile_table): rows keyed by the shape bucket
+// (ceil(M/128), ceil(N/64), ceil(K/64)) and the SM count they were measured on. A product whose
+// bucket is in the table gets the measured tile and split; every other product the cost model below.
+struct TileTableRow {
+    int mb, nb, kb, sms, tile, split;
+};
+static std::mutex g_tile_table_mu;
+static std::vector<TileTableRow> g_tile_table;
+
+static bool tile_table_lookup(int M, int N, int K, int sms, int* tile_cfg, int* split_k) {
+    std::lock_guard<std::mutex> lock(g_tile_table_mu);
+    if (g_tile_table.empty()) return false;
+    const int mb = ceil_div(M, 128), nb = ceil_div(N, 64), kb = ceil_div(K, 64);
+    for (const TileTableRow& r : g_tile_table) {
+        if (r.mb == mb && r.nb == nb && r.kb == kb && r.sms == sms) {
+            *tile_cfg = r.tile;
+            *split_k = r.split;
+            return true;
+        }
+    }
+    return false;
+}
+
 static void select_tile_impl(int M, int N, int K, int sms, int* tile_cfg, int* split_k) {
+    if (tile_table_lookup(M, N, K, sms, tile_cfg, split_k)) return;
     const int kb_total = ceil_div(K, BK);
     const int cfgs[3] = {WMMA_OPS_TILE_128x256, WMMA_OPS_TILE_128x128, WMMA_OPS_TILE_128x64};
     double best_time = 0.0;
@@ -642,6 +667,27 @@ extern "C" int wmma_ops_select_tile(int M, int N, int K, int num_sms, int* tile_
     WB_REQUIRE(tile_cfg != nullptr && split_k != nullptr, WMMA_OPS_ERR_INVALID,
                "select_tile: null output pointer");
     wb::select_tile_impl(M, N, K, num_sms > 0 ? num_sms : 148, tile_cfg, split_k);
+    return WMMA_OPS_OK;
+}
+
+extern "C" int wmma_ops_set_tile_table(const int* rows, int n_rows) {
+    using namespace wb;
+    WB_REQUIRE(n_rows >= 0 && (n_rows == 0 || rows != nullptr), WMMA_OPS_ERR_INVALID, "set_tile_table: bad arguments");
+    std::vector<TileTableRow> table;
+    table.reserve(n_rows);
+    for (int i = 0; i < n_rows; ++i) {
+        const int* r = rows + 6 * i;
+        const int M = r[0], N = r[1], K = r[2], sms = r[3], tile = r[4], split = r[5];
+        WB_REQUIRE(M >= 1 && N >= 1 && K >= 1 && sms >= 1, WMMA_OPS_ERR_INVALID,
+                   "set_tile_table: row %d has a non-positive shape or SM count", i);
+        WB_REQUIRE(tile_bn(tile) > 0, WMMA_OPS_ERR_INVALID, "set_tile_table: row %d names tile %d", i, tile);
+        WB_REQUIRE(split >= 1 && split <= ceil_div(K, BK) && (split == 1 || tile != WMMA_OPS_TILE_256x256_PAIR),
+                   WMMA_OPS_ERR_INVALID, "set_tile_table: row %d has split_k=%d (1..K/64; the CTA-pair tile has no split)", i,
+                   split);
+        table.push_back({ceil_div(M, 128), ceil_div(N, 64), ceil_div(K, 64), sms, tile, split});
+    }
+    std::lock_guard<std::mutex> lock(g_tile_table_mu);
+    g_tile_table.swap(table);
     return WMMA_OPS_OK;
 }
 

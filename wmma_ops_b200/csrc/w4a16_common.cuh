@@ -157,10 +157,10 @@ inline size_t w4_counter_bytes(int tiles) {
 // CTAs of a cluster each take one part of K. The decode kernel needs no workspace.
 struct W4DecodePlan {
     int kb_total, n_tiles, gpu, units, ksplit, clusters, upc, ncg, slot_bytes, pitch, depth;
-    int red_off, out_off, bar_off, smem_bytes, grid;
+    int seg_kb, xs_off, x_pitch, ss_off, ss_pitch, alias_red, red_off, out_off, bar_off, smem_bytes, grid;
 };
 
-W4DecodePlan w4_decode_plan(int M, int N, int K, int out_mode, int sms);
+W4DecodePlan w4_decode_plan(int M, int N, int K, int group_size, int out_mode, int sms);
 int w4_decode_launch(const W4Params& p, const W4DecodePlan& d, cudaStream_t stream);
 
 }  // namespace wb

@@ -89,12 +89,18 @@ struct ScPlan {
     int ksplit;        // CTAs per cluster
     int upc;           // units per chunk (a chunk is what one pass over K accumulates in registers)
     int depth;         // ring slots per warp
-    int slot_bytes;    // bytes of one slot
+    int slot_bytes;    // bytes of one slot (the packed weights of a chunk's columns for one k-block)
+    int seg_kb;        // k-blocks per segment: the activations and scales of one segment are staged at a time
+    int xs_off;        // staged activations [M][x_pitch bytes]
+    int x_pitch;       // seg_kb * 128 + 16 bytes (the 16 spread the rows of a quad over the banks)
+    int ss_off;        // staged fp16 scales [groups of the segment][ss_pitch bytes]
+    int ss_pitch;
     int pitch;         // floats per token row of the reduction tiles
     int red_off;       // byte offsets into dynamic shared memory
     int out_off;
     int bar_off;
     int smem_bytes;
+    int alias_red;     // 1: the reduction tiles lie over the ring (every cluster has one chunk)
     int overlap;       // 1: launched as a programmatic dependent launch
 };
 
@@ -105,39 +111,6 @@ __device__ __forceinline__ int sc_group_col(int v0, int j) {
     // fused gate/up: unit v is the 16 gate columns 128*(v/4) + 16*(v%4) and the up columns 64 further on
     const int v = v0 + (j >> 1);
     return (v >> 2) * 128 + (v & 3) * 16 + (j & 1) * 64;
-}
-
-struct ScXFrag {
-    uint4 a[2];  // X[token][64 kb + 16 t .. + 15]: eight (k, k+1) words, two per MMA
-};
-
-template <int ROWS>
-__device__ __forceinline__ void sc_load_x(const W4Params& p, const __half* xrow, int kb, int g, ScXFrag (&x)[ROWS]) {
-    const uint4 zero = make_uint4(0u, 0u, 0u, 0u);
-#pragma unroll
-    for (int o = 0; o < ROWS; ++o) {
-        x[o].a[0] = x[o].a[1] = zero;
-        if (g + 8 * o < p.M) {
-            const uint4* src = reinterpret_cast<const uint4*>(xrow + static_cast<size_t>(8 * o) * p.K + kb * W4_BK);
-            x[o].a[0] = __ldg(src);
-            x[o].a[1] = __ldg(src + 1);
-        }
-    }
-}
-
-// The fp16 scales of k-block kb for this lane's columns g and g + 8 of every group of the chunk that
-// starts at unit v0 (low / high half of one register per group; zero past the chunk or past N).
-template <int NCG, bool GU>
-__device__ __forceinline__ void sc_load_scales(const W4Params& p, int v0, int ncg, int kb, int g, uint32_t (&sc)[NCG]) {
-    const int grp = p.group_shift >= 0 ? (kb >> p.group_shift) : (kb / p.group_kb);
-    const unsigned short* srow = reinterpret_cast<const unsigned short*>(p.scales) + static_cast<size_t>(grp) * p.N;
-#pragma unroll
-    for (int j = 0; j < NCG; ++j) {
-        const int c = sc_group_col<GU>(v0, j) + g;
-        const uint32_t lo = (j < ncg && c < p.N) ? __ldg(srow + c) : 0u;
-        const uint32_t hi = (j < ncg && c + 8 < p.N) ? __ldg(srow + c + 8) : 0u;
-        sc[j] = lo | (hi << 16);
-    }
 }
 
 __device__ __forceinline__ void sc_store_out(const W4Params& p, int tok, int col, float v) {
@@ -152,10 +125,6 @@ __device__ __forceinline__ void sc_store_out(const W4Params& p, int tok, int col
 template <int ROWS, int NCG, int JB, bool GU>
 __global__ void __launch_bounds__(SC_THREADS, 1) w4a16_decode_kernel(const W4Params p, const ScPlan pl) {
     static_assert(NCG % JB == 0, "column groups are worked on in whole blocks");
-    // With two token groups the registers do not hold a second set of activation fragments: the
-    // activations of a k-block are then loaded at the top of its own iteration (ahead of the wait for
-    // the weights) instead of one iteration earlier.
-    constexpr bool XPRE = ROWS == 1;
     extern __shared__ __align__(128) uint8_t sc_smem[];
     const uint32_t smem_base = smem_u32(sc_smem);
     const int tid = threadIdx.x;
@@ -185,20 +154,21 @@ __global__ void __launch_bounds__(SC_THREADS, 1) w4a16_decode_kernel(const W4Par
     const uint32_t ring = smem_base + static_cast<uint32_t>(warp * pl.depth * pl.slot_bytes);
     const uint8_t* ring_ptr = sc_smem + warp * pl.depth * pl.slot_bytes;
     const uint32_t bars = smem_base + static_cast<uint32_t>(pl.bar_off) + static_cast<uint32_t>(warp * pl.depth) * 8u;
+    const uint32_t stage_bar = smem_base + static_cast<uint32_t>(pl.bar_off) + static_cast<uint32_t>(SC_WARPS * pl.depth) * 8u;
 
     if (lane == 0) {
         for (int s = 0; s < pl.depth; ++s) mbar_init(bars + 8u * s, 1);
+        if (warp == 0) mbar_init(stage_bar, 1);
         fence_barrier_init();
         fence_proxy_async_smem();
     }
-    __syncwarp();
+    __syncthreads();
     SC_MARK(1);
 
-    // The next item to request: chunk rq_v0 (its first unit), k-block index rq_i of this warp.
+    // The next weight segment to request: chunk rq_v0 (its first unit), k-block index rq_i of this warp.
     int rq_v0 = u0, rq_i = 0, rq_slot = 0;
-    // Requests the next item into slot rq_slot and moves on. Lane 0 only; false when nothing is left.
-    auto request = [&]() -> bool {
-        if (nkb == 0 || rq_v0 >= u1) return false;
+    auto request = [&]() {  // lane 0; does nothing when no item is left
+        if (nkb == 0 || rq_v0 >= u1) return;
         const int kb = k0 + warp + SC_WARPS * rq_i;
         const int nun = (u1 - rq_v0 < pl.upc ? u1 - rq_v0 : pl.upc);
         const int ncg = nun * pl.gpu;
@@ -218,40 +188,109 @@ __global__ void __launch_bounds__(SC_THREADS, 1) w4a16_decode_kernel(const W4Par
             rq_v0 += pl.upc;
         }
         if (++rq_slot == pl.depth) rq_slot = 0;
-        return true;
     };
-    // The first k-block's activations and scales are requested before the weight segments: once
-    // ~150 KB of bulk copies per SM are queued in the memory system, a small load issued behind them
-    // waits until they have drained (measured: 3.3 us instead of 0.6 us to the first usable block).
-    // With overlapped decode launches (programmatic dependent launch; the caller promises that the
-    // packed weights are not produced by the kernels just before this one) it is the other way
-    // round: the CTA may be here while the previous kernel is still finishing, so it requests its
-    // weights first and touches activations, scales and output only after griddepcontrol.wait.
-    const __half* xrow = p.X + static_cast<size_t>(g) * p.K + 16 * t;
-    ScXFrag x_first[ROWS];
-    uint32_t sc_first[NCG];
-    const int ncg_first = (u1 - u0 < pl.upc ? u1 - u0 : pl.upc) * pl.gpu;
-    if (!pl.overlap) {
-        asm volatile("griddepcontrol.wait;" ::: "memory");
-        if (nkb > 0) {
-            if (XPRE) sc_load_x<ROWS>(p, xrow, k0 + warp, g, x_first);
-            sc_load_scales<NCG, GU>(p, u0, ncg_first, k0 + warp, g, sc_first);
+
+    // Activations and scales are staged in shared memory one K segment at a time, ahead of the weight
+    // requests. Activations: one bulk copy per row (the segment's part of it), issued by warp 0.
+    // Scales: plain 8-byte loads by all threads, issued before any bulk copy of the CTA and stored to
+    // shared memory once the weight requests are out. What was tried before: plain loads inside the
+    // k-loop (issued behind ~150 KB of queued bulk copies per SM, a small load took 3.5 us to come
+    // back), one bulk copy per activation row per k-block, and one bulk copy per scale group (the SM
+    // accepts bulk copies at about one per 20 cycles per issuing lane, so 30 small copies from one
+    // warp cost more than all the weight requests).
+    uint32_t stage_phase = 0;
+    bool ok = true;  // false once a bounded wait gave up
+    constexpr int SC_STAGE_LOADS = 4;  // 8-byte scale loads per thread and round
+    // Stages the scales of chunk (v0, nun) and k-blocks [ks0, ks1), and with with_x the activations.
+    // All threads. `before_x` and `after_x` run after the scale loads are issued, around the
+    // activation copies, and before the loaded values are needed.
+    auto stage = [&](int v0, int nun, int ks0, int ks1, bool with_x, auto&& before_x, auto&& after_x) {
+        const int ncg = nun * pl.gpu;
+        const int c0 = sc_group_col<GU>(v0, 0);
+        int span = sc_group_col<GU>(v0, ncg - 1) + SC_GROUP_COLS - c0;  // columns from the chunk's first to its last
+        if (c0 + span > p.N) span = p.N - c0;
+        const int g0 = p.group_shift >= 0 ? (ks0 >> p.group_shift) : (ks0 / p.group_kb);
+        const int g1 = p.group_shift >= 0 ? ((ks1 - 1) >> p.group_shift) : ((ks1 - 1) / p.group_kb);
+        const int ng = g1 - g0 + 1;
+        const int per_row = span >> 2;          // 8-byte words per scale row (span is a multiple of 8... of 4 scales)
+        const int words = ng * per_row;
+        bool first = true;
+        for (int base = 0; base < words; base += SC_THREADS * SC_STAGE_LOADS) {
+            uint32_t lo[SC_STAGE_LOADS], hi[SC_STAGE_LOADS];
+            int dst[SC_STAGE_LOADS];
+#pragma unroll
+            for (int q = 0; q < SC_STAGE_LOADS; ++q) {
+                const int e = base + q * SC_THREADS + tid;
+                dst[q] = -1;
+                if (e < words) {
+                    const int gi = e / per_row;
+                    const int c4 = e - gi * per_row;
+                    const __half* src = p.scales + static_cast<size_t>(g0 + gi) * p.N + c0 + 4 * c4;
+                    asm volatile("ld.global.nc.v2.u32 {%0, %1}, [%2];" : "=r"(lo[q]), "=r"(hi[q]) : "l"(src));
+                    dst[q] = pl.ss_off + gi * pl.ss_pitch + c4 * 8;
+                }
+            }
+            if (first) {
+                before_x();
+                if (with_x && warp == 0) {
+                    const uint32_t xbytes = static_cast<uint32_t>((ks1 - ks0) * 128);
+                    if (lane == 0) mbar_arrive_expect_tx(stage_bar, static_cast<uint32_t>(p.M) * xbytes);
+                    __syncwarp();
+                    if (lane < p.M)
+                        bulk_load_1d(smem_base + static_cast<uint32_t>(pl.xs_off + lane * pl.x_pitch),
+                                     p.X + static_cast<size_t>(lane) * p.K + ks0 * W4_BK, xbytes, stage_bar);
+                }
+                after_x();
+                first = false;
+            }
+#pragma unroll
+            for (int q = 0; q < SC_STAGE_LOADS; ++q)
+                if (dst[q] >= 0) *reinterpret_cast<uint2*>(sc_smem + dst[q]) = make_uint2(lo[q], hi[q]);
         }
-    }
-    if (lane == 0) {
-        for (int s = 0; s < pl.depth; ++s)
-            if (!request()) break;
+        __syncthreads();  // the scales are in place for every warp
+        if (with_x) {
+            if (ok && !mbar_wait(stage_bar, stage_phase)) {
+                sc_report(p.status, warp, 30000);
+                ok = false;
+            }
+            stage_phase ^= 1u;
+        }
+    };
+    const int seg_first_end = k0 + pl.seg_kb < k1 ? k0 + pl.seg_kb : k1;
+    const bool one_segment = seg_first_end == k1;
+    const int nun_first = (u1 - u0 < pl.upc ? u1 - u0 : pl.upc);
+    auto first_requests = [&]() {
+        if (lane == 0)
+            for (int s = 0; s < pl.depth; ++s) request();
+    };
+    // With overlapped decode launches (programmatic dependent launch; the caller promises that the
+    // packed weights and their scales are not produced by the kernels just before this one) the CTA
+    // may be here while the previous kernel of the stream is still finishing: it loads its scales and
+    // requests its weights first, and touches activations and output only after griddepcontrol.wait.
+    // In an ordinary launch the wait returns at once, and the activation copies go out ahead of the
+    // weights.
+    auto nothing = [] {};
+    if (pl.overlap) {
+        stage(u0, nun_first, k0, seg_first_end, true,
+              [&] {
+                  first_requests();
+                  asm volatile("griddepcontrol.wait;" ::: "memory");
+              },
+              nothing);
+    } else {
+        asm volatile("griddepcontrol.wait;" ::: "memory");
+        stage(u0, nun_first, k0, seg_first_end, true, nothing, first_requests);
     }
     SC_MARK(2);
-    if (pl.overlap) {
-        asm volatile("griddepcontrol.wait;" ::: "memory");
-        if (nkb > 0) {
-            if (XPRE) sc_load_x<ROWS>(p, xrow, k0 + warp, g, x_first);
-            sc_load_scales<NCG, GU>(p, u0, ncg_first, k0 + warp, g, sc_first);
-        }
-    }
 
-    bool ok = true;
+    // this lane's activation words within a staged row: token g (and g + 8), k 16t .. 16t+15 of a
+    // k-block; tokens past M read the last row (their MMA columns are never stored)
+    int x_lane_off[ROWS];
+#pragma unroll
+    for (int o = 0; o < ROWS; ++o) {
+        const int row = g + 8 * o < p.M ? g + 8 * o : p.M - 1;
+        x_lane_off[o] = pl.xs_off + row * pl.x_pitch + t * 32;
+    }
     int slot = 0;
     uint32_t phase = 0;
 
@@ -259,6 +298,9 @@ __global__ void __launch_bounds__(SC_THREADS, 1) w4a16_decode_kernel(const W4Par
         const int nun = (u1 - v0 < pl.upc ? u1 - v0 : pl.upc);
         const int ncg = nun * pl.gpu;
         const int col0 = sc_group_col<GU>(v0, 0);  // without GU the chunk's columns are contiguous from here
+        int sc_lane_off[NCG];                      // this lane's scale of group j within a staged scale row
+#pragma unroll
+        for (int j = 0; j < NCG; ++j) sc_lane_off[j] = (sc_group_col<GU>(v0, j) - col0 + g) * 2;
 
         float acc[NCG][ROWS][4];
 #pragma unroll
@@ -266,131 +308,126 @@ __global__ void __launch_bounds__(SC_THREADS, 1) w4a16_decode_kernel(const W4Par
 #pragma unroll
             for (int o = 0; o < ROWS; ++o) acc[j][o][0] = acc[j][o][1] = acc[j][o][2] = acc[j][o][3] = 0.f;
 
-        // activations and scales of the chunk's first k-block; the scales of columns g and g + 8 of
-        // group j share one register (low / high half)
-        ScXFrag x_next[ROWS];
-        uint32_t sc_next[NCG];
-        auto load_scales = [&](int kb) { sc_load_scales<NCG, GU>(p, v0, ncg, kb, g, sc_next); };
-        if (nkb > 0) {
-            if (v0 == u0) {
-                if (XPRE) {
-#pragma unroll
-                    for (int o = 0; o < ROWS; ++o) x_next[o] = x_first[o];
-                }
-#pragma unroll
-                for (int j = 0; j < NCG; ++j) sc_next[j] = sc_first[j];
-            } else {
-                if (XPRE) sc_load_x<ROWS>(p, xrow, k0 + warp, g, x_next);
-                load_scales(k0 + warp);
+        int i = 0;  // index of this warp's next k-block within the chunk
+        for (int ks0 = k0; ks0 < k1; ks0 += pl.seg_kb) {
+            const int ks1 = ks0 + pl.seg_kb < k1 ? ks0 + pl.seg_kb : k1;
+            if (!(v0 == u0 && ks0 == k0)) {
+                // a new segment or chunk: every warp is done with what is staged, then it is replaced
+                // (the activations only if they change)
+                __syncthreads();
+                stage(v0, nun, ks0, ks1, !one_segment, nothing, nothing);
             }
-        }
+            const int g_first = p.group_shift >= 0 ? (ks0 >> p.group_shift) : (ks0 / p.group_kb);
 
 #pragma unroll 1
-        for (int i = 0; i < nkb; ++i) {
-            ScXFrag x[ROWS];
-            uint32_t sc[NCG];
-            if (XPRE) {
-#pragma unroll
-                for (int o = 0; o < ROWS; ++o) x[o] = x_next[o];
-            } else {
-                sc_load_x<ROWS>(p, xrow, k0 + warp + SC_WARPS * i, g, x);
-            }
-#pragma unroll
-            for (int j = 0; j < NCG; ++j) sc[j] = sc_next[j];
-            if (i + 1 < nkb) {
-                const int kbn = k0 + warp + SC_WARPS * (i + 1);
-                if (XPRE) sc_load_x<ROWS>(p, xrow, kbn, g, x_next);
-                load_scales(kbn);
-            }
+            for (; k0 + warp + SC_WARPS * i < ks1; ++i) {
+                const int kb = k0 + warp + SC_WARPS * i;
 #ifdef SC_TIMELINE
-            const long long tw0 = clock64();
+                const long long tw0 = clock64();
 #endif
-            if (ok && !mbar_wait(bars + 8u * slot, phase)) {
-                sc_report(p.status, warp, i);
-                ok = false;
-            }
-            ok = __all_sync(0xffffffffu, ok);
-            if (i == 0 && v0 == u0) SC_MARK(3);
+                if (ok && !mbar_wait(bars + 8u * slot, phase)) {
+                    sc_report(p.status, warp, i);
+                    ok = false;
+                }
+                ok = __all_sync(0xffffffffu, ok);
+                if (i == 0 && v0 == u0) SC_MARK(3);
 #ifdef SC_TIMELINE
-            if (lane == 0 && i > 0) sc_timeline[(blockIdx.x * 16 + warp) * 8 + 6] += clock64() - tw0;
-            if (lane == 0 && i == 0) sc_timeline[(blockIdx.x * 16 + warp) * 8 + 6] = 0;
+                if (lane == 0 && i > 0) sc_timeline[(blockIdx.x * 16 + warp) * 8 + 6] += clock64() - tw0;
+                if (lane == 0 && i == 0) sc_timeline[(blockIdx.x * 16 + warp) * 8 + 6] = 0;
 #endif
-#ifdef SC_NOCOMPUTE
-            if (false) {
-#else
-            if (ok) {
-#endif
-                const float zero4[4] = {0.f, 0.f, 0.f, 0.f};
-                const uint2* sl = reinterpret_cast<const uint2*>(ring_ptr + slot * pl.slot_bytes);
+                if (ok) {
+                    const uint2* sl = reinterpret_cast<const uint2*>(ring_ptr + slot * pl.slot_bytes);
+                    const int grel = (p.group_shift >= 0 ? (kb >> p.group_shift) : (kb / p.group_kb)) - g_first;
+                    const uint8_t* ssc = sc_smem + pl.ss_off + grel * pl.ss_pitch;
+                    uint4 xa[ROWS][2];
 #pragma unroll
-                for (int jb = 0; jb < NCG; jb += JB) {
-                    if (jb < ncg) {
-                        // Weights are the MMA's A operand (rows = columns g and g + 8 of a group), the
-                        // activations its B operand (columns = tokens): the expanded pairs land in the
-                        // A registers as computed and the B registers are the words of X as loaded.
-                        // All JB groups of the block are worked on whether or not the chunk has them (no
-                        // branch between the MMAs; a group past the chunk's last reads stale shared
-                        // memory and its sums are never stored).
-                        uint2 wa[JB], wb[JB];
+                    for (int o = 0; o < ROWS; ++o) {
+                        const uint4* xs = reinterpret_cast<const uint4*>(sc_smem + x_lane_off[o] + (kb - ks0) * 128);
+                        xa[o][0] = xs[0];
+                        xa[o][1] = xs[1];
+                    }
+                    const float zero4[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
-                        for (int jj = 0; jj < JB; ++jj) {
-                            wa[jj] = sl[(16 * (jb + jj) + g) * 4 + t];      // words 2t, 2t+1: k 16t .. 16t+15
-                            wb[jj] = sl[(16 * (jb + jj) + 8 + g) * 4 + t];
-                        }
-                        float d[JB][ROWS][4];
-#pragma unroll
-                        for (int ks = 0; ks < 4; ++ks) {
+                    for (int jb = 0; jb < NCG; jb += JB) {
+                        if (jb < ncg) {
+                            // Weights are the MMA's A operand (rows = columns g and g + 8 of a group),
+                            // the activations its B operand (columns = tokens): the expanded pairs land
+                            // in the A registers as computed and the B registers are the words of X as
+                            // loaded. All JB groups of the block are worked on whether or not the chunk
+                            // has them (no branch between the MMAs; a group past the chunk's last reads
+                            // stale shared memory and its sums are never stored).
+                            uint2 wa[JB], wb[JB];
 #pragma unroll
                             for (int jj = 0; jj < JB; ++jj) {
+                                wa[jj] = sl[(16 * (jb + jj) + g) * 4 + t];      // words 2t, 2t+1: k 16t .. 16t+15
+                                wb[jj] = sl[(16 * (jb + jj) + 8 + g) * 4 + t];
+                            }
+                            float d[JB][ROWS][4];
+                            // The expansion of k-step ks + 1 is written between the MMAs of k-step ks.
+                            uint32_t ea[2][JB][4];
+                            auto expand = [&](int jj, int ks, uint32_t (&e)[4]) {
                                 const uint32_t ua = (ks & 2) ? wa[jj].y : wa[jj].x;
                                 const uint32_t ub = (ks & 2) ? wb[jj].y : wb[jj].x;
-                                uint32_t a0, a1, a2, a3;
-                                sc_expand_pairs((ks & 1) ? (ua >> 8) : ua, a0, a2);
-                                sc_expand_pairs((ks & 1) ? (ub >> 8) : ub, a1, a3);
+                                sc_expand_pairs((ks & 1) ? (ua >> 8) : ua, e[0], e[2]);
+                                sc_expand_pairs((ks & 1) ? (ub >> 8) : ub, e[1], e[3]);
+                            };
 #pragma unroll
-                                for (int o = 0; o < ROWS; ++o) {
-                                    const uint4 xv = x[o].a[ks >> 1];
-                                    const uint32_t b0 = (ks & 1) ? xv.z : xv.x;
-                                    const uint32_t b1 = (ks & 1) ? xv.w : xv.y;
-                                    if (ks == 0) mma_m16n8k16(d[jj][o], a0, a1, a2, a3, b0, b1, zero4);
-                                    else mma_m16n8k16(d[jj][o], a0, a1, a2, a3, b0, b1, d[jj][o]);
+                            for (int jj = 0; jj < JB; ++jj) expand(jj, 0, ea[0][jj]);
+#pragma unroll
+                            for (int ks = 0; ks < 4; ++ks) {
+#pragma unroll
+                                for (int jj = 0; jj < JB; ++jj) {
+#pragma unroll
+                                    for (int o = 0; o < ROWS; ++o) {
+                                        const uint4 xv = xa[o][ks >> 1];
+                                        const uint32_t b0 = (ks & 1) ? xv.z : xv.x;
+                                        const uint32_t b1 = (ks & 1) ? xv.w : xv.y;
+                                        const uint32_t(&e)[4] = ea[ks & 1][jj];
+                                        if (ks == 0) mma_m16n8k16(d[jj][o], e[0], e[1], e[2], e[3], b0, b1, zero4);
+                                        else mma_m16n8k16(d[jj][o], e[0], e[1], e[2], e[3], b0, b1, d[jj][o]);
+                                    }
+                                    if (ks < 3) expand(jj, ks + 1, ea[(ks + 1) & 1][jj]);
                                 }
                             }
-                        }
 #pragma unroll
-                        for (int jj = 0; jj < JB; ++jj) {
-                            const __half2 sc2 = bits_h2(sc[jb + jj]);
-                            const float f0 = __low2float(sc2), f1 = __high2float(sc2);
+                            for (int jj = 0; jj < JB; ++jj) {
+                                // the scales of columns g and g + 8 of the group (stale past N: those
+                                // columns are never stored)
+                                const float f0 = __half2float(*reinterpret_cast<const __half*>(ssc + sc_lane_off[jb + jj]));
+                                const float f1 = __half2float(*reinterpret_cast<const __half*>(ssc + sc_lane_off[jb + jj] + 16));
 #pragma unroll
-                            for (int o = 0; o < ROWS; ++o) {
-                                acc[jb + jj][o][0] = fmaf(d[jj][o][0], f0, acc[jb + jj][o][0]);
-                                acc[jb + jj][o][1] = fmaf(d[jj][o][1], f0, acc[jb + jj][o][1]);
-                                acc[jb + jj][o][2] = fmaf(d[jj][o][2], f1, acc[jb + jj][o][2]);
-                                acc[jb + jj][o][3] = fmaf(d[jj][o][3], f1, acc[jb + jj][o][3]);
+                                for (int o = 0; o < ROWS; ++o) {
+                                    acc[jb + jj][o][0] = fmaf(d[jj][o][0], f0, acc[jb + jj][o][0]);
+                                    acc[jb + jj][o][1] = fmaf(d[jj][o][1], f0, acc[jb + jj][o][1]);
+                                    acc[jb + jj][o][2] = fmaf(d[jj][o][2], f1, acc[jb + jj][o][2]);
+                                    acc[jb + jj][o][3] = fmaf(d[jj][o][3], f1, acc[jb + jj][o][3]);
+                                }
                             }
                         }
                     }
                 }
-            }
-            // every lane's reads of the slot have returned: their values were used by the MMAs above
-            __syncwarp();
-            if (lane == 0 && ok) request();
-            if (++slot == pl.depth) {
-                slot = 0;
-                phase ^= 1u;
+                // every lane's reads of the slot have returned: their values were used by the MMAs above
+                __syncwarp();
+                if (ok && lane == 0) request();
+                if (++slot == pl.depth) {
+                    slot = 0;
+                    phase ^= 1u;
+                }
             }
         }
         if (v0 == u0) SC_MARK(4);
 
         // ---- this warp's tile of the chunk: [token][column], tokens below M only
+        if (pl.alias_red) __syncthreads();  // the tiles lie over the ring: every warp has read its last slot
         float* mine = red + static_cast<size_t>(warp) * p.M * pl.pitch;
 #pragma unroll
         for (int j = 0; j < NCG; ++j) {
             if (j < ncg) {
+                const int cj = sc_group_col<GU>(v0, j) - col0;  // the group's place in the chunk's span of columns
 #pragma unroll
                 for (int o = 0; o < ROWS; ++o) {
                     const int tok = 8 * o + 2 * t;
-                    float* dst = mine + tok * pl.pitch + 16 * j + g;
+                    float* dst = mine + tok * pl.pitch + (GU ? 16 * j : cj) + g;
                     if (tok < p.M) {
                         dst[0] = acc[j][o][0];
                         dst[8] = acc[j][o][2];
@@ -474,8 +511,9 @@ static int sc_ncg(int M, int longest_groups) {
     return longest_groups <= 5 ? 5 : 8;
 }
 
-W4DecodePlan w4_decode_plan(int M, int N, int K, int out_mode, int sms) {
+W4DecodePlan w4_decode_plan(int M, int N, int K, int group_size, int out_mode, int sms) {
     W4DecodePlan d;
+    const int group_kb = group_size / W4_BK;
     d.kb_total = K / W4_BK;
     d.n_tiles = (N + W4_TILE_N - 1) / W4_TILE_N;
     d.gpu = out_mode == WMMA_OPS_W4_OUT_F16_SILU_MUL ? 2 : 1;
@@ -505,23 +543,68 @@ W4DecodePlan w4_decode_plan(int M, int N, int K, int out_mode, int sms) {
     const int cols = d.upc * d.gpu * SC_GROUP_COLS;
     d.slot_bytes = d.upc * d.gpu * SC_GROUP_BYTES;
     d.pitch = cols + 4;  // 4 or 20 modulo 32: a quad's rows 2t land in different banks
+    // the chunk's span of columns, first to last: its own columns, or with the fused gate/up output
+    // the tiles its units touch
+    const int span = d.gpu == 1 ? cols : ((d.upc + 2) / 4 + 1) * W4_TILE_N;
+    d.ss_pitch = (span * 2 + 15) / 16 * 16;
     const int red_bytes = SC_WARPS * M * d.pitch * 4;
-    const int out_bytes = M * d.pitch * 4;
+    const int out_bytes = (M * d.pitch * 4 + 127) / 128 * 128;
+    const int bar_bytes = (SC_WARPS * 16 + 1) * 8 + 120;
     // one group block past the last slot may be read (and ignored) by the kernel: keep it inside the allocation
-    const int fixed = red_bytes + out_bytes + SC_WARPS * 16 * 8 + 1024 + 8 * SC_GROUP_BYTES;
-    int depth = (SC_SMEM_LIMIT - fixed) / (SC_WARPS * d.slot_bytes);
+    const int slack = 8 * SC_GROUP_BYTES;
     const int kb_cta = (d.kb_total + d.ksplit - 1) / d.ksplit;
     const int items = ((kb_cta + SC_WARPS - 1) / SC_WARPS) * chunks;  // per warp
-    if (depth > items) depth = items;
+    // Segments are whole rounds of the 16 warps and whole scale groups. The longest segment that
+    // leaves the ring two slots per warp (or all items, if fewer) is taken; with one chunk per
+    // cluster nothing is requested into the ring once its last slot has been read, so the reduction
+    // tiles may lie over it, which is taken when it buys a deeper ring.
+    int unit_kb = SC_WARPS;
+    while (unit_kb % group_kb != 0) unit_kb += SC_WARPS;
+    const int want = items < 2 ? items : 2;
+    int seg = (kb_cta + unit_kb - 1) / unit_kb * unit_kb;
+    int depth = 0;
+    for (;;) {
+        const int x_bytes = (M * (seg * 128 + 16) + 127) / 128 * 128;
+        const int ss_bytes = (((seg + group_kb - 1) / group_kb + 1) * d.ss_pitch + 127) / 128 * 128;
+        auto depth_for = [&](bool alias) {
+            const int fixed = x_bytes + ss_bytes + out_bytes + bar_bytes + slack + 256 + (alias ? 0 : red_bytes);
+            const int room = SC_SMEM_LIMIT - fixed;
+            int dd = room > 0 ? room / (SC_WARPS * d.slot_bytes) : 0;
+            if (alias && SC_WARPS * dd * d.slot_bytes + slack < red_bytes) dd = 0;  // the tiles must fit under the ring
+            return dd < items ? dd : items;
+        };
+        depth = depth_for(false);
+        d.alias_red = 0;
+        if (chunks == 1 && depth < items) {
+            const int da = depth_for(true);
+            if (da > depth) {
+                depth = da;
+                d.alias_red = 1;
+            }
+        }
+        if (depth >= want || seg <= unit_kb) break;
+        seg = (seg / 2 + unit_kb - 1) / unit_kb * unit_kb;  // halve, in whole units
+    }
     if (depth > 16) depth = 16;
     if (depth < 1) depth = 1;
     d.depth = depth;
+    d.seg_kb = seg;
+    d.x_pitch = seg * 128 + 16;
+    const int x_bytes = (M * d.x_pitch + 127) / 128 * 128;
+    const int ss_bytes = (((seg + group_kb - 1) / group_kb + 1) * d.ss_pitch + 127) / 128 * 128;
     const int ring_bytes = SC_WARPS * depth * d.slot_bytes;
-    d.red_off = (ring_bytes + 127) / 128 * 128;
-    d.out_off = d.red_off + (red_bytes + 127) / 128 * 128;
-    d.bar_off = d.out_off + (out_bytes + 127) / 128 * 128;
-    d.smem_bytes = d.bar_off + SC_WARPS * depth * 8;
-    if (d.smem_bytes < ring_bytes + 8 * SC_GROUP_BYTES) d.smem_bytes = ring_bytes + 8 * SC_GROUP_BYTES;
+    const int ring_span = (ring_bytes + slack + 127) / 128 * 128;
+    if (d.alias_red) {
+        d.red_off = 0;
+        d.xs_off = ring_span > red_bytes ? ring_span : (red_bytes + 127) / 128 * 128;
+    } else {
+        d.red_off = ring_span;
+        d.xs_off = d.red_off + (red_bytes + 127) / 128 * 128;
+    }
+    d.ss_off = d.xs_off + x_bytes;
+    d.out_off = d.ss_off + ss_bytes;
+    d.bar_off = d.out_off + out_bytes;
+    d.smem_bytes = d.bar_off + bar_bytes;
     d.grid = d.clusters * d.ksplit;
     return d;
 }
@@ -577,6 +660,12 @@ int w4_decode_launch(const W4Params& p, const W4DecodePlan& d, cudaStream_t stre
     pl.upc = d.upc;
     pl.depth = d.depth;
     pl.slot_bytes = d.slot_bytes;
+    pl.seg_kb = d.seg_kb;
+    pl.xs_off = d.xs_off;
+    pl.x_pitch = d.x_pitch;
+    pl.ss_off = d.ss_off;
+    pl.ss_pitch = d.ss_pitch;
+    pl.alias_red = d.alias_red;
     pl.pitch = d.pitch;
     pl.red_off = d.red_off;
     pl.out_off = d.out_off;
@@ -602,15 +691,18 @@ extern "C" int wmma_ops_debug_timeline(long long* host_out) {
 }
 #endif
 
-extern "C" int wmma_ops_w4a16_decode_plan(int M, int N, int K, int out_mode, int num_sms, int* plan) {
+extern "C" int wmma_ops_w4a16_decode_plan(int M, int N, int K, int group_size, int out_mode, int num_sms, int* plan) {
     using namespace wb;
     WB_REQUIRE(plan != nullptr, WMMA_OPS_ERR_INVALID, "w4a16_decode_plan: null output pointer");
     WB_REQUIRE(M >= 1 && M <= W4_STREAM_MAX_M && N >= 8 && N % 8 == 0 && K >= 64 && K % 64 == 0, WMMA_OPS_ERR_INVALID,
                "w4a16_decode_plan: needs 1 <= M <= %d, N %% 8 == 0, K %% 64 == 0 (got %d, %d, %d)", W4_STREAM_MAX_M, M, N, K);
     WB_REQUIRE(out_mode != WMMA_OPS_W4_OUT_F16_SILU_MUL || N % 128 == 0, WMMA_OPS_ERR_INVALID,
                "w4a16_decode_plan: the fused gate/up output needs N %% 128 == 0 (got N=%d)", N);
-    const W4DecodePlan d = w4_decode_plan(M, N, K, out_mode, num_sms > 0 ? num_sms : 148);
-    const int v[11] = {d.grid, d.clusters, d.ksplit, d.units, d.gpu, d.upc, d.depth, d.slot_bytes, d.pitch, d.smem_bytes, d.ncg};
-    for (int i = 0; i < 11; ++i) plan[i] = v[i];
+    WB_REQUIRE(group_size >= 64 && group_size % 64 == 0 && K % group_size == 0, WMMA_OPS_ERR_INVALID,
+               "w4a16_decode_plan: group_size must be a multiple of 64 that divides K (got %d)", group_size);
+    const W4DecodePlan d = w4_decode_plan(M, N, K, group_size, out_mode, num_sms > 0 ? num_sms : 148);
+    const int v[14] = {d.grid, d.clusters, d.ksplit, d.units, d.gpu, d.upc, d.depth, d.slot_bytes, d.pitch, d.smem_bytes, d.ncg,
+                       d.alias_red, d.seg_kb, d.x_pitch};
+    for (int i = 0; i < 14; ++i) plan[i] = v[i];
     return WMMA_OPS_OK;
 }

@@ -713,7 +713,7 @@ extern "C" int wmma_ops_w4a16_gemm_ex(const void* A, const void* qweight, const 
     p.counters = nullptr;
     if (w4_use_stream(M, N, K, split_k)) {
         // decode: one pass over the packed weights, every CTA owning a range of columns
-        const W4DecodePlan dp = w4_decode_plan(M, N, K, out_mode, sms);
+        const W4DecodePlan dp = w4_decode_plan(M, N, K, group_size, out_mode, sms);
         p.n_tiles = dp.n_tiles;
         p.t_tiles = 1;
         p.kb_total = dp.kb_total;

@@ -160,7 +160,7 @@ def _launch_gemm(A, B, C_in, C_out, M, N, K, alpha, beta, tile_cfg, split_k) -> 
     with _device_guard(dev):
         ws_ptr, ws_bytes = None, 0
         if tile_cfg == _lib.TILE_AUTO and split_k == 0 and M > 0 and N > 0 and K > 0:
-            cfg, sk = select_tile(M, N, K, _sm_count(dev))
+            cfg, sk = select_tile(M, N, K, _sm_count(dev))   # measured table first, then the cost model
             tile_cfg, split_k = cfg, sk
         if split_k > 1:
             need = lib.wmma_ops_gemm_workspace_bytes(M, N, K, split_k)
@@ -174,6 +174,7 @@ def _launch_gemm(A, B, C_in, C_out, M, N, K, alpha, beta, tile_cfg, split_k) -> 
 
 
 _sm_counts: dict = {}
+_table_checked = False
 
 
 def _sm_count(device: torch.device) -> int:
@@ -195,6 +196,13 @@ def select_tile(M: int, N: int, K: int, num_sms: int = 148) -> Tuple[int, int]:
     """(tile_cfg, split_k) for an MxNxK product: the Blackwell counterpart of the reference's
     select_optimal_tile (wmma_tile_selection.hpp:30-66) and split_k::compute_config
     (wmma_xor_swizzle.hpp:293-332). Pure host arithmetic; works without a GPU."""
+    global _table_checked
+    if not _table_checked:
+        # a measured tile table (WMMA_OPS_TILE_TABLE, or the one shipped with the package) takes
+        # precedence over the built-in cost model for the shape buckets it holds
+        _table_checked = True
+        from . import tune
+        tune.install_from_env()
     cfg = ctypes.c_int(0)
     sk = ctypes.c_int(0)
     _lib.check(_lib.load().wmma_ops_select_tile(M, N, K, num_sms, ctypes.byref(cfg), ctypes.byref(sk)))

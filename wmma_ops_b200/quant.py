@@ -83,8 +83,8 @@ def set_w4a16_overlap(enable: bool) -> None:
     """Switches overlapped decode launches on or off (off by default, process-wide): with it on,
     matmul_w4a16 products with up to 16 rows start fetching their packed weights while the previous
     kernel of the stream is still finishing (programmatic dependent launch) and wait for it before
-    reading the activations. Only for weights that are not produced by the kernels queued just
-    before the call, which is the case in decode."""
+    reading the activations. Only for weights and scales that are not produced by the kernels queued
+    just before the call, which is the case in decode."""
     _lib.check(_lib.load().wmma_ops_set_w4a16_overlap(1 if enable else 0))
 
 
