@@ -21,6 +21,14 @@ import threading
 import time
 from pathlib import Path
 
+if int(os.environ.get("WORLD_SIZE", "1")) > 1:
+    # Multi-rank runs: NCCL's communicator lines (ranks, transport, NVLS) are the record that N ranks
+    # really ran on N GPUs. They go to stderr; stdout carries exactly one JSON line. Set before torch
+    # (and with it NCCL) is loaded, over whatever the launcher exported.
+    os.environ["NCCL_DEBUG"] = "INFO"
+    os.environ["NCCL_DEBUG_SUBSYS"] = "INIT"
+    os.environ["NCCL_DEBUG_FILE"] = "/dev/stderr"
+
 import torch
 
 ROOT = Path(__file__).resolve().parent
@@ -386,30 +394,41 @@ def measure_layer(w, dev, rank, world, steps):
             layer = sharded.ShardedDecoderLinears(local, world=world, reduce_dtype=rdt)
             record(label, *eager(layer))
             del layer
-        sw = None
-        try:
-            sw = SwitchAllReduce(tokens, 4096, dev)
-        except Exception as e:  # no symmetric memory / multicast on this system
-            out["nvswitch"] = {"error": f"{type(e).__name__}: {str(e)[:200]}"}
-        if sw is not None:
-            # partial outputs written into symmetric memory by the row-parallel GEMMs and summed
-            # through the NVSwitch by the library's own kernel (barriers inside the kernel)
-            for label, part in (("nvswitch_fp16_partials", torch.float16), ("nvswitch_fp32_partials", torch.float32)):
-                try:
-                    layer = sharded.ShardedDecoderLinears(local, world=world, reduce_dtype=part, switch=sw)
-                except Exception as e:
-                    out[label] = {"error": f"{type(e).__name__}: {str(e)[:200]}"}
-                    continue
-                record(label, *eager(layer))
-                # replayed from a CUDA graph: at 4-8 GPUs the per-rank kernels are shorter than the host
-                # needs to launch them one by one
-                try:
-                    run, outs = graphed(layer)
-                    record(label + "_cuda_graph", run, outs)
-                    del run, outs
-                except Exception as e:
-                    out[label + "_cuda_graph"] = {"error": f"{type(e).__name__}: {str(e)[:200]}"}
-                del layer
+        # partial outputs written into symmetric memory by the row-parallel GEMMs and summed through the
+        # NVSwitch by the library's own kernel (one launch per sum, rank barriers inside the kernel):
+        # fp16 partials summed in place, or fp32 partials summed into an fp16 buffer
+        for label, part in (("nvswitch_fp16_partials", torch.float16), ("nvswitch_fp32_partials", torch.float32)):
+            try:
+                sw = SwitchAllReduce(tokens, 4096, dev, partial_dtype=part)
+                layer = sharded.ShardedDecoderLinears(local, world=world, reduce_dtype=part, switch=sw)
+            except Exception as e:  # no symmetric memory / multicast on this system
+                out[label] = {"error": f"{type(e).__name__}: {str(e)[:200]}"}
+                continue
+            record(label, *eager(layer))
+            # replayed from a CUDA graph: at 4-8 GPUs the per-rank kernels are shorter than the host
+            # needs to launch them one by one
+            try:
+                run, outs = graphed(layer)
+                record(label + "_cuda_graph", run, outs)
+                del run, outs
+            except Exception as e:
+                out[label + "_cuda_graph"] = {"error": f"{type(e).__name__}: {str(e)[:200]}"}
+            del layer
+            # two token chunks on two streams: the sum of one chunk (32 CTAs) runs beside the GEMMs of
+            # the other (the remaining SMs)
+            try:
+                sw.max_ctas = 32
+                w.set_sm_margin(32)
+                layer = sharded.ShardedDecoderLinears(local, world=world, reduce_dtype=part, switch=sw, chunks=2)
+                run, outs = graphed(layer)
+                record(label + "_2chunks_cuda_graph", run, outs)
+                del run, outs, layer
+            except Exception as e:
+                out[label + "_2chunks_cuda_graph"] = {"error": f"{type(e).__name__}: {str(e)[:200]}"}
+            sw.max_ctas = 0
+            w.set_sm_margin(0)
+            del sw
+            torch.cuda.synchronize()
         # last, because capturing NCCL collectives changes how later eager collectives behave
         try:
             layer = sharded.ShardedDecoderLinears(local, world=world, reduce_dtype=torch.float16)
@@ -492,11 +511,6 @@ def run_ours(args):
     dev = torch.device("cuda", local_rank)
     torch.cuda.set_device(dev)
     if world > 1:
-        # stdout carries exactly one JSON line; NCCL's communicator lines (ranks, transport, NVLS)
-        # are wanted as a record of the run, so they go to stderr
-        os.environ.setdefault("NCCL_DEBUG", "INFO")
-        os.environ.setdefault("NCCL_DEBUG_SUBSYS", "INIT")
-        os.environ.setdefault("NCCL_DEBUG_FILE", "/dev/stderr")
         import torch.distributed as dist
         dist.init_process_group("nccl", device_id=dev)
     peaks = load_peaks()

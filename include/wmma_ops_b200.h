@@ -174,16 +174,18 @@ int wmma_ops_w4a16_gemm(const void* A, const void* qweight, const void* scales, 
 /* wmma_ops_w4a16_gemm with a fused output stage (no counterpart in the reference):
  *   WMMA_OPS_W4_OUT_F32           C fp32 [M,N] = acc                      (what wmma_ops_w4a16_gemm does)
  *   WMMA_OPS_W4_OUT_F16           C fp16 [M,N] = half(alpha * acc)
- *   WMMA_OPS_W4_OUT_F16_SILU_MUL  C fp16 [M,N/2] = half(alpha * silu(gate) * up), where in every
+ *   WMMA_OPS_W4_OUT_F16_SILU_MUL  C fp16 [M,N/2] = half(alpha * silu(in_scale * gate) * (in_scale * up)), where in every
  *                                 128-column tile of the weight the first 64 columns are gate columns
  *                                 and the last 64 the up columns of the same 64 outputs (N % 128 == 0).
+ * in_scale (used by the last mode only; pass 1 otherwise) stands for a scale of the activations
+ * that the caller did not apply: A may then be the unscaled tensor.
  * With M > 16 the fp16 modes run without partial sums (split_k 0 or 1). */
 #define WMMA_OPS_W4_OUT_F32 0
 #define WMMA_OPS_W4_OUT_F16 1
 #define WMMA_OPS_W4_OUT_F16_SILU_MUL 2
 int wmma_ops_w4a16_gemm_ex(const void* A, const void* qweight, const void* scales, void* C, int M, int N,
-                           int K, int group_size, int split_k, int out_mode, float alpha, void* workspace,
-                           size_t workspace_bytes, int* status, void* stream);
+                           int K, int group_size, int split_k, int out_mode, float alpha, float in_scale,
+                           void* workspace, size_t workspace_bytes, int* status, void* stream);
 
 /* Sum of an fp16 buffer over the ranks of one NVSwitch domain, in place, for the row-parallel
  * outputs of the sharded layer (no counterpart in the reference, which is single-GPU).
@@ -195,6 +197,25 @@ int wmma_ops_w4a16_gemm_ex(const void* A, const void* qweight, const void* scale
  * accumulation) and stores the result to all ranks (multimem.st). max_ctas <= 0: all SMs. */
 int wmma_ops_multimem_allreduce_f16(void* multicast_ptr, size_t n_halves, int rank, int world, int max_ctas,
                                     void* stream);
+
+/* The same sum as one self-contained launch: the rank barriers before and after the reduction are
+ * made inside the kernel with flags in symmetric memory (no counterpart in the reference).
+ *   mc_in / mc_out  multicast addresses of buffers every rank holds in symmetric memory. With
+ *                   in_is_f32 = 0, mc_in holds n_values fp16 partial outputs and is summed in
+ *                   place (mc_out == mc_in). With in_is_f32 = 1, mc_in holds n_values fp32
+ *                   partials and the sums are written as fp16 to mc_out.
+ *   flag_ptrs_dev   device array of `world` pointers, entry r being rank r's copy of a
+ *                   zero-initialised symmetric buffer of wmma_ops_switch_allreduce_flag_bytes()
+ *                   bytes that is used for nothing else.
+ *   channel         0..3; calls that may be in flight at the same time need different channels.
+ *   max_ctas        CTAs per rank (<= 0: 64); all ranks must pass the same value.
+ * Every rank calls it with the same arguments on a stream on which its partial outputs have been
+ * written; when the call has completed on a rank, that rank's copy of the output holds all sums.
+ * A rank that does not arrive within about a second makes the others record {5, rank, block,
+ * missing rank} in `status` and finish with an incomplete sum instead of hanging. */
+size_t wmma_ops_switch_allreduce_flag_bytes(void);
+int wmma_ops_switch_allreduce(const void* mc_in, void* mc_out, size_t n_values, int in_is_f32, int rank, int world,
+                              const void* flag_ptrs_dev, int channel, int max_ctas, int* status, void* stream);
 
 /* Flash-attention forward: O = softmax(scale * Q K^T [+ causal mask]) V per (b,h).
  * Q, K, V, O are [B,H,S,D] fp16 contiguous; the signature documented in the reference's

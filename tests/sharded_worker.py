@@ -1,8 +1,16 @@
 """Worker for tests/test_sharded_multi_gpu.py: run under torch.distributed.run with one rank per
-GPU (NCCL). Every rank computes the sharded layer on 256 tokens with full layer shapes and
-compares the all-reduced outputs with the single-process CPU oracle."""
+GPU (NCCL). Every rank computes the sharded layer on 1024 tokens with full layer shapes; EVERY rank
+compares its own copy of the all-reduced outputs with the single-process CPU oracle (rank 0
+computes it and broadcasts it). The accuracy gate is the workload's: relative Frobenius error
+<= 1e-3 against the fp32 oracle for the variants that claim it; the fp16-partials variants are
+held to their measured error plus margin and the number is printed either way.
+
+A failure on one rank is recorded, not raised: every rank still reaches the final collectives and
+releases its symmetric-memory buffers before the process group is destroyed, so that no rank exits
+while its memory is bound to the multicast object and its peers wait on it."""
 import os
 import sys
+import traceback
 from pathlib import Path
 
 import torch
@@ -15,58 +23,95 @@ from oracle import gemm as og  # noqa: E402
 from oracle import layer as olayer  # noqa: E402
 from wmma_ops_b200 import sharded  # noqa: E402
 
+GATE = 1e-3          # the workload's tolerance (attn_out and mlp_out)
+FP16_PARTIALS = 2e-3  # partial outputs rounded to fp16 before the sum: measured below 1e-3 / 1.3e-3
+
 
 def main():
     rank, local_rank, world = int(os.environ["RANK"]), int(os.environ["LOCAL_RANK"]), int(os.environ["WORLD_SIZE"])
     dev = torch.device("cuda", local_rank)
     torch.cuda.set_device(dev)
     dist.init_process_group("nccl", device_id=dev)
-    weights = olayer.make_layer_weights(seed=21)
-    g = torch.Generator().manual_seed(5)
-    x = torch.randn(1024, 4096, generator=g).to(torch.float16)
-    local = {k: (c.to(dev), s.to(dev)) for k, (c, s) in sharded.shard_layer_weights(weights, rank, world).items()}
     ok = True
-    w.set_sm_margin(16)
-    for rdt, chunks, tol in ((torch.float32, 1, 1e-3), (torch.float16, 1, 3e-3), (torch.float16, 2, 3e-3)):
-        layer = sharded.ShardedDecoderLinears(local, world=world, reduce_dtype=rdt, chunks=chunks)
-        attn, mlp = layer(x.to(dev))
-        torch.cuda.synchronize()
-        w.check_status(dev)
-        if rank == 0:
-            ref_attn, ref_mlp = olayer.layer_ref(x, weights)
-            e1 = og.rel_frobenius(attn.float(), ref_attn)
-            e2 = og.rel_frobenius(mlp.float(), ref_mlp)
-            print(f"world={world} reduce={rdt} attn_err={e1:.2e} mlp_err={e2:.2e}", flush=True)
-            ok = ok and e1 < tol and e2 < 2 * tol
-    # the same layer with the partial outputs summed through the NVSwitch by the library's own
-    # multimem kernel (symmetric memory); skipped where the system offers no NVLink multicast
+    layer = sw16 = sw32 = None
     try:
-        from wmma_ops_b200.collective import SwitchAllReduce
-        sw = SwitchAllReduce(1024, 4096, dev)
-    except Exception as e:  # no symmetric memory / multicast
-        sw = None
+        weights = olayer.make_layer_weights(seed=21)
+        g = torch.Generator().manual_seed(5)
+        T = 1024
+        x = torch.randn(T, 4096, generator=g).to(torch.float16)
+        refs = torch.empty((2, T, 4096), dtype=torch.float32, device=dev)
         if rank == 0:
-            print(f"switch all-reduce unavailable: {type(e).__name__}: {str(e)[:200]}", flush=True)
-    if sw is not None:
-        for chunks in (1, 2):
-            layer = sharded.ShardedDecoderLinears(local, world=world, reduce_dtype=torch.float16, chunks=chunks,
-                                                  switch=sw)
-            attn, mlp = layer(x.to(dev))
+            torch.set_num_threads(max(1, os.cpu_count() or 1))
+            ra, rm = olayer.layer_ref(x, weights)
+            refs[0].copy_(ra)
+            refs[1].copy_(rm)
+        dist.broadcast(refs, 0)
+        ref_attn, ref_mlp = refs[0].cpu(), refs[1].cpu()
+        local = {k: (c.to(dev), s.to(dev)) for k, (c, s) in sharded.shard_layer_weights(weights, rank, world).items()}
+        del weights
+        xd = x.to(dev)
+
+        def check(label, layer, tol_attn, tol_mlp):
+            attn, mlp = layer(xd)
             torch.cuda.synchronize()
             w.check_status(dev)
+            errs = torch.tensor([og.rel_frobenius(attn.float().cpu(), ref_attn), og.rel_frobenius(mlp.float().cpu(), ref_mlp)],
+                                dtype=torch.float64, device=dev)
+            dist.all_reduce(errs, op=dist.ReduceOp.MAX)       # every rank holds its own copy: the worst one counts
+            e1, e2 = errs.tolist()
             if rank == 0:
-                ref_attn, ref_mlp = olayer.layer_ref(x, weights)
-                e1 = og.rel_frobenius(attn.float(), ref_attn)
-                e2 = og.rel_frobenius(mlp.float(), ref_mlp)
-                print(f"world={world} switch chunks={chunks} attn_err={e1:.2e} mlp_err={e2:.2e}", flush=True)
-                ok = ok and e1 < 3e-3 and e2 < 6e-3
+                print(f"world={world} {label}: attn_err={e1:.2e} mlp_err={e2:.2e} (max over ranks)", flush=True)
+            return e1 < tol_attn and e2 < tol_mlp
+
+        w.set_sm_margin(16)
+        for rdt, chunks, tol in ((torch.float32, 1, GATE), (torch.float16, 1, FP16_PARTIALS), (torch.float16, 2, FP16_PARTIALS)):
+            layer = sharded.ShardedDecoderLinears(local, world=world, reduce_dtype=rdt, chunks=chunks)
+            ok = check(f"nccl reduce={rdt} chunks={chunks}", layer, tol, tol) and ok
+            layer = None
+        w.set_sm_margin(0)
+        # the same layer with the partial outputs summed through the NVSwitch by the library's own
+        # kernel (symmetric memory, barriers inside the kernel); skipped where the system offers no
+        # NVLink multicast
+        try:
+            from wmma_ops_b200.collective import SwitchAllReduce
+            sw16 = SwitchAllReduce(T, 4096, dev, partial_dtype=torch.float16)
+            sw32 = SwitchAllReduce(T, 4096, dev, partial_dtype=torch.float32)
+        except Exception as e:  # no symmetric memory / multicast
+            sw16 = sw32 = None
+            if rank == 0:
+                print(f"switch all-reduce unavailable: {type(e).__name__}: {str(e)[:200]}", flush=True)
+        if sw16 is not None:
+            for label, sw, rdt, chunks, tol in (("switch fp32 partials", sw32, torch.float32, 1, GATE),
+                                                ("switch fp16 partials", sw16, torch.float16, 1, FP16_PARTIALS),
+                                                ("switch fp16 partials, 2 chunks", sw16, torch.float16, 2, FP16_PARTIALS),
+                                                ("switch fp32 partials, 2 chunks", sw32, torch.float32, 2, GATE)):
+                if chunks > 1:
+                    sw.max_ctas = 32
+                    w.set_sm_margin(32)
+                layer = sharded.ShardedDecoderLinears(local, world=world, reduce_dtype=rdt, chunks=chunks, switch=sw)
+                for _ in range(2):      # twice: the barrier epochs advance, nothing is reset between calls
+                    ok = check(label, layer, tol, tol) and ok
+                layer = None
+                sw.max_ctas = 0
+                w.set_sm_margin(0)
+    except Exception:
+        ok = False
+        print(f"rank {rank} failed:\n{traceback.format_exc()}", flush=True)
+    # every rank gets here, whatever happened above
     flag = torch.tensor([1 if ok else 0], device=dev)
-    dist.broadcast(flag, 0)
-    dist.barrier()
-    dist.destroy_process_group()
+    try:
+        torch.cuda.synchronize()
+        dist.all_reduce(flag, op=dist.ReduceOp.MIN)
+        layer = None
+        sw16 = sw32 = None
+        torch.cuda.synchronize()
+        dist.barrier()
+    finally:
+        dist.destroy_process_group()
+    passed = flag.item() == 1
     if rank == 0:
-        print("SHARDED_PASS" if ok else "SHARDED_FAIL", flush=True)
-    sys.exit(0 if flag.item() == 1 else 1)
+        print("SHARDED_PASS" if passed else "SHARDED_FAIL", flush=True)
+    sys.exit(0 if passed else 1)
 
 
 if __name__ == "__main__":

@@ -25,4 +25,5 @@ def test_sharded_layer_nccl(cuda, world):
            "--master-addr", "127.0.0.1", "--master-port", str(_free_port()), str(worker)]
     res = subprocess.run(cmd, capture_output=True, text=True, timeout=600,
                          env={**__import__("os").environ, "NCCL_NVLS_ENABLE": "0"})
+    print(res.stdout[-3000:])
     assert res.returncode == 0 and "SHARDED_PASS" in res.stdout, res.stdout[-2000:] + res.stderr[-2000:]

@@ -13,6 +13,7 @@
 //
 // The caller synchronises the ranks before (all partial products written) and after (all slices
 // stored) with the symmetric-memory barrier; this kernel itself waits on nobody.
+#include <cuda_fp16.h>
 #include <cuda_runtime.h>
 
 #include "host_common.cuh"
@@ -73,6 +74,180 @@ extern "C" int wmma_ops_multimem_allreduce_f16(void* multicast_ptr, size_t n_hal
     if (static_cast<size_t>(ctas) > want) ctas = static_cast<int>(want);
     multimem_allreduce_f16_kernel<<<ctas, 512, 0, static_cast<cudaStream_t>(stream)>>>(
         static_cast<uint4*>(multicast_ptr), first, n_vec);
+    WB_CHECK_CUDA(cudaGetLastError());
+    return WMMA_OPS_OK;
+}
+
+// ---------------------------------------------------------------------------------------------
+// The same sum as one self-contained launch: the two rank barriers that bracket the reduction
+// (every rank's partial output is written / every rank's slice is stored everywhere) are made
+// inside the kernel with flags in symmetric memory, instead of two extra barrier launches per sum.
+// Two input forms: fp16 partials summed in place, or fp32 partials summed into a separate fp16
+// buffer (twice the bytes on the way in, no fp16 rounding of the partial outputs).
+//
+// Flags. Every rank holds, per channel, SW_MAX_CTAS x SW_MAX_WORLD arrival words and SW_MAX_CTAS
+// epoch words. CTA b of rank r announces step e by writing e to word [b][r] of every rank's flags
+// (peer stores, release at system scope) and waits until its own words [b][0..world) have all
+// reached e (acquire loads). The epoch of a CTA lives in device memory and advances by two per
+// launch, so nothing is ever reset and a launch replayed from a CUDA graph keeps working. A CTA
+// only ever waits for the same CTA of the other ranks; the kernel as a whole completes when all of
+// its CTAs have, which is when every rank has stored every part of its slice.
+// Every wait is bounded (about a second); on expiry the CTA records {code 5, rank, block, peer} in
+// the status word and carries on, so a rank that never arrives costs a wrong result, not a hang.
+namespace wb {
+
+constexpr int SW_MAX_CTAS = 128;
+constexpr int SW_MAX_WORLD = 16;
+constexpr int SW_CHANNEL_WORDS = SW_MAX_CTAS * SW_MAX_WORLD + SW_MAX_CTAS;
+constexpr int SW_CHANNELS = 4;
+constexpr long long SW_WAIT_CYCLES = 2000000000ll;
+
+__device__ __forceinline__ void st_release_sys(uint32_t* p, uint32_t v) {
+    asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+__device__ __forceinline__ uint32_t ld_acquire_sys(const uint32_t* p) {
+    uint32_t v;
+    asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+    return v;
+}
+
+__device__ __forceinline__ uint4 multimem_ld_reduce_f32(const uint4* p) {
+    uint4 v;
+    asm volatile("multimem.ld_reduce.relaxed.sys.global.add.v4.f32 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
+                 : "l"(p)
+                 : "memory");
+    return v;
+}
+
+__device__ __forceinline__ uint32_t pack_h2(uint32_t a_bits, uint32_t b_bits) {
+    const __half2 h = __floats2half2_rn(__uint_as_float(a_bits), __uint_as_float(b_bits));
+    return *reinterpret_cast<const uint32_t*>(&h);
+}
+
+// Step `e` of CTA blockIdx.x: threads 0..world-1 each tell one peer and wait for that peer.
+__device__ __forceinline__ void sw_rank_barrier(uint32_t* const* flag_ptrs, int channel, int rank, int world, uint32_t e,
+                                                int* status) {
+    __syncthreads();  // this CTA's earlier stores are ordered before the fence of the signalling threads
+    const int r = threadIdx.x;
+    if (r < world) {
+        const size_t word = static_cast<size_t>(channel) * SW_CHANNEL_WORDS + static_cast<size_t>(blockIdx.x) * SW_MAX_WORLD;
+        __threadfence_system();
+        st_release_sys(flag_ptrs[r] + word + rank, e);
+        const uint32_t* mine = flag_ptrs[rank] + word + r;
+        const long long t0 = clock64();
+        uint32_t spins = 0;
+        while (static_cast<int>(ld_acquire_sys(mine) - e) < 0) {
+            __nanosleep(64);
+            if ((++spins & 0xff) == 0 && clock64() - t0 > SW_WAIT_CYCLES) {
+                if (status != nullptr && atomicCAS(status, 0, 5) == 0) {
+                    status[1] = rank;
+                    status[2] = static_cast<int>(blockIdx.x);
+                    status[3] = r;
+                }
+                break;
+            }
+        }
+    }
+    __syncthreads();
+}
+
+// F32_IN: partials are fp32 at mc_in and the sums go, as fp16, to mc_out (16 bytes of output per two
+// 16-byte input vectors); otherwise fp16 partials at mc_in are summed in place (mc_out == mc_in).
+// first / count are in units of 16 bytes of output.
+template <bool F32_IN>
+__global__ void __launch_bounds__(512) switch_allreduce_kernel(const uint4* mc_in, uint4* mc_out, size_t first, size_t count,
+                                                               uint32_t* const* flag_ptrs, int channel, int rank, int world,
+                                                               int* status) {
+    __shared__ uint32_t epoch_s;
+    uint32_t* epoch_word = flag_ptrs[rank] + static_cast<size_t>(channel) * SW_CHANNEL_WORDS + SW_MAX_CTAS * SW_MAX_WORLD +
+                           blockIdx.x;
+    if (threadIdx.x == 0) epoch_s = *epoch_word;
+    __syncthreads();
+    const uint32_t e = epoch_s;
+    sw_rank_barrier(flag_ptrs, channel, rank, world, e + 1, status);  // every rank's partial output is written
+
+    const size_t stride = static_cast<size_t>(gridDim.x) * blockDim.x;
+    size_t i = static_cast<size_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+    if (F32_IN) {
+        constexpr int U = AR_UNROLL / 2;
+        const uint4* in = mc_in + 2 * first;
+        uint4* out = mc_out + first;
+        for (; i < count; i += U * stride) {
+            uint4 a[U], b[U];
+#pragma unroll
+            for (int u = 0; u < U; ++u) {
+                const size_t k = i + u * stride;
+                if (k < count) {
+                    a[u] = multimem_ld_reduce_f32(in + 2 * k);
+                    b[u] = multimem_ld_reduce_f32(in + 2 * k + 1);
+                }
+            }
+#pragma unroll
+            for (int u = 0; u < U; ++u) {
+                const size_t k = i + u * stride;
+                if (k < count) {
+                    uint4 o;
+                    o.x = pack_h2(a[u].x, a[u].y);
+                    o.y = pack_h2(a[u].z, a[u].w);
+                    o.z = pack_h2(b[u].x, b[u].y);
+                    o.w = pack_h2(b[u].z, b[u].w);
+                    multimem_st(out + k, o);
+                }
+            }
+        }
+    } else {
+        uint4* base = mc_out + first;
+        for (; i < count; i += AR_UNROLL * stride) {
+            uint4 v[AR_UNROLL];
+#pragma unroll
+            for (int u = 0; u < AR_UNROLL; ++u)
+                if (i + u * stride < count) v[u] = multimem_ld_reduce_f16(base + i + u * stride);
+#pragma unroll
+            for (int u = 0; u < AR_UNROLL; ++u)
+                if (i + u * stride < count) multimem_st(base + i + u * stride, v[u]);
+        }
+    }
+    sw_rank_barrier(flag_ptrs, channel, rank, world, e + 2, status);  // every rank's slice is stored everywhere
+    if (threadIdx.x == 0) *epoch_word = e + 2;
+}
+
+}  // namespace wb
+
+extern "C" size_t wmma_ops_switch_allreduce_flag_bytes(void) {
+    return static_cast<size_t>(wb::SW_CHANNELS) * wb::SW_CHANNEL_WORDS * sizeof(uint32_t);
+}
+
+extern "C" int wmma_ops_switch_allreduce(const void* mc_in, void* mc_out, size_t n_values, int in_is_f32, int rank, int world,
+                                         const void* flag_ptrs_dev, int channel, int max_ctas, int* status, void* stream) {
+    using namespace wb;
+    WB_REQUIRE(mc_in != nullptr && mc_out != nullptr && flag_ptrs_dev != nullptr, WMMA_OPS_ERR_INVALID,
+               "switch_allreduce: null pointer");
+    WB_REQUIRE(world >= 1 && world <= SW_MAX_WORLD && rank >= 0 && rank < world, WMMA_OPS_ERR_INVALID,
+               "switch_allreduce: rank %d / world %d out of range (at most %d ranks)", rank, world, SW_MAX_WORLD);
+    WB_REQUIRE(channel >= 0 && channel < SW_CHANNELS, WMMA_OPS_ERR_INVALID, "switch_allreduce: channel %d not in 0..%d", channel,
+               SW_CHANNELS - 1);
+    WB_REQUIRE(reinterpret_cast<uintptr_t>(mc_in) % 16 == 0 && reinterpret_cast<uintptr_t>(mc_out) % 16 == 0 && n_values % 8 == 0,
+               WMMA_OPS_ERR_INVALID, "switch_allreduce: buffers must be 16-byte aligned and a multiple of 8 values long");
+    WB_REQUIRE(in_is_f32 || mc_in == mc_out, WMMA_OPS_ERR_INVALID, "switch_allreduce: fp16 partials are summed in place");
+    const size_t total = n_values / 8;  // 16-byte units of output
+    const size_t base = total / world, extra = total % world;
+    const size_t first = static_cast<size_t>(rank) * base + (static_cast<size_t>(rank) < extra ? rank : extra);
+    const size_t count = base + (static_cast<size_t>(rank) < extra ? 1 : 0);
+    // every rank launches the same number of CTAs (they pair up across ranks), also for an empty slice
+    int ctas = max_ctas > 0 ? max_ctas : 64;
+    if (ctas > SW_MAX_CTAS) ctas = SW_MAX_CTAS;
+    const size_t want = (base + 1 + 511) / 512;
+    if (static_cast<size_t>(ctas) > want) ctas = static_cast<int>(want);
+    if (ctas < 1) ctas = 1;
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    uint32_t* const* flags = static_cast<uint32_t* const*>(flag_ptrs_dev);
+    if (in_is_f32)
+        switch_allreduce_kernel<true><<<ctas, 512, 0, s>>>(static_cast<const uint4*>(mc_in), static_cast<uint4*>(mc_out), first,
+                                                           count, flags, channel, rank, world, status);
+    else
+        switch_allreduce_kernel<false><<<ctas, 512, 0, s>>>(static_cast<const uint4*>(mc_in), static_cast<uint4*>(mc_out), first,
+                                                            count, flags, channel, rank, world, status);
     WB_CHECK_CUDA(cudaGetLastError());
     return WMMA_OPS_OK;
 }

@@ -597,7 +597,8 @@ static void select_tile_impl(int M, int N, int K, int sms, int* tile_cfg, int* s
         // fixed per-unit cost: pipeline fill + epilogue drain, in clocks
         const double unit_cost = kblock_cost(bn) * kb_per + 600.0 + 2.0 * bn;
         double t = waves * unit_cost;
-        if (split > 1) t += 0.02 * split * (static_cast<double>(M) * N / sms);  // reduce pass
+        // the reduce pass: its traffic, and a second launch (about 3 us of clocks) that small products never win back
+        if (split > 1) t += 0.02 * split * (static_cast<double>(M) * N / sms) + 6000.0;
         if (i == 0 || t < best_time) {
             best_time = t;
             best_cfg = cfgs[i];

@@ -25,6 +25,7 @@ struct W4Params {
     __half* C16;       // fp16 output (out_mode 1: [M,N]; out_mode 2: [M,N/2])
     int out_mode;      // 0: C = acc; 1: C16 = half(alpha*acc); 2: C16 = half(alpha*silu(gate)*up)
     float alpha;
+    float in_scale;    // out_mode 2 only: gate and up are multiplied by this before silu(gate) * up (a scale of the input, folded in)
     float* partials;   // [tiles][split][BT][128]
     int* counters;     // [tiles]
     int M, N, K;

@@ -486,8 +486,8 @@ __global__ void __launch_bounds__(SC_THREADS, 1) w4a16_decode_kernel(const W4Par
                         const int tok = e / nout;
                         const int r = e - tok * nout;
                         const int u = r >> 4, c = r & 15;
-                        const float gate = total(tok, 32 * u + c);
-                        const float up = total(tok, 32 * u + 16 + c);
+                        const float gate = p.in_scale * total(tok, 32 * u + c);
+                        const float up = p.in_scale * total(tok, 32 * u + 16 + c);
                         const int v = v0 + u;
                         const int fcol = (v >> 2) * 64 + (v & 3) * 16 + c;
                         const float act = p.alpha * (gate / (1.f + __expf(-gate))) * up;

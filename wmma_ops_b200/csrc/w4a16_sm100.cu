@@ -385,8 +385,8 @@ w4a16_gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_const
                         for (int j = 0; j < CH; ++j) {
                             uint32_t ub;
                             asm volatile("ld.shared.u32 %0, [%1];" : "=r"(ub) : "r"(out_stage + (j * 64 + row) * 4) : "memory");
-                            const float gte = __uint_as_float(v[j]);
-                            const float act = p.alpha * (gte / (1.f + __expf(-gte))) * __uint_as_float(ub);
+                            const float gte = p.in_scale * __uint_as_float(v[j]);
+                            const float act = p.alpha * (gte / (1.f + __expf(-gte))) * (p.in_scale * __uint_as_float(ub));
                             const int t = t0 + c * CH + j;
                             if (t < p.M && f < ldo) p.C16[static_cast<size_t>(t) * ldo + f] = __float2half_rn(act);
                         }
@@ -655,12 +655,12 @@ extern "C" size_t wmma_ops_w4a16_workspace_bytes(int M, int N, int K, int split_
 extern "C" int wmma_ops_w4a16_gemm(const void* A, const void* qweight, const void* scales, void* C, int M,
                                    int N, int K, int group_size, int split_k, void* workspace,
                                    size_t workspace_bytes, int* status, void* stream_) {
-    return wmma_ops_w4a16_gemm_ex(A, qweight, scales, C, M, N, K, group_size, split_k, WMMA_OPS_W4_OUT_F32, 1.0f,
+    return wmma_ops_w4a16_gemm_ex(A, qweight, scales, C, M, N, K, group_size, split_k, WMMA_OPS_W4_OUT_F32, 1.0f, 1.0f,
                                   workspace, workspace_bytes, status, stream_);
 }
 
 extern "C" int wmma_ops_w4a16_gemm_ex(const void* A, const void* qweight, const void* scales, void* C, int M,
-                                      int N, int K, int group_size, int split_k, int out_mode, float alpha,
+                                      int N, int K, int group_size, int split_k, int out_mode, float alpha, float in_scale,
                                       void* workspace, size_t workspace_bytes, int* status, void* stream_) {
     using namespace wb;
     WB_REQUIRE(out_mode >= WMMA_OPS_W4_OUT_F32 && out_mode <= WMMA_OPS_W4_OUT_F16_SILU_MUL, WMMA_OPS_ERR_INVALID,
@@ -695,6 +695,7 @@ extern "C" int wmma_ops_w4a16_gemm_ex(const void* A, const void* qweight, const 
     p.C16 = static_cast<__half*>(C);
     p.out_mode = out_mode;
     p.alpha = alpha;
+    p.in_scale = in_scale;
     p.M = M;
     p.N = N;
     p.K = K;

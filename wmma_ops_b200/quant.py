@@ -102,7 +102,7 @@ def interleave_gate_up(codes: torch.Tensor, scales: torch.Tensor) -> Tuple[torch
 
 def matmul_w4a16(A: torch.Tensor, qweight: torch.Tensor, scales: torch.Tensor, group_size: int = 128,
                  split_k: int = 0, out_dtype: torch.dtype = torch.float32, alpha: float = 1.0,
-                 epilogue: str = "none", out: Optional[torch.Tensor] = None) -> torch.Tensor:
+                 epilogue: str = "none", out: Optional[torch.Tensor] = None, in_scale: float = 1.0) -> torch.Tensor:
     """C [M,N] = A fp16 [M,K] @ dequant(qweight, scales); the weights are expanded inside the kernel,
     never written to memory. split_k=0 lets the library choose: up to 16 rows go to the decode
     kernel (every CTA owns a range of columns and streams their packed weights over all of K; exact
@@ -111,7 +111,8 @@ def matmul_w4a16(A: torch.Tensor, qweight: torch.Tensor, scales: torch.Tensor, g
 
     out_dtype=torch.float32 (default) returns the fp32 accumulators. out_dtype=torch.float16 returns
     half(alpha * acc). epilogue="silu_mul" (weights prepared with interleave_gate_up) returns
-    half(alpha * silu(gate) * up) of shape [M, N/2]. `out`, if given, is the contiguous tensor of that
+    half(alpha * silu(in_scale * gate) * (in_scale * up)) of shape [M, N/2]; in_scale stands for a scale
+    of A that the caller left out (A @ W is linear in A). `out`, if given, is the contiguous tensor of that
     shape and dtype the result is written to (for example a buffer in symmetric memory)."""
     _require(A.is_cuda and qweight.is_cuda and scales.is_cuda, "Inputs must be CUDA tensors")
     _require(A.device == qweight.device and A.device == scales.device, "Inputs must be on same device")
@@ -119,6 +120,7 @@ def matmul_w4a16(A: torch.Tensor, qweight: torch.Tensor, scales: torch.Tensor, g
     _require(scales.dtype == torch.float16 and scales.dim() == 2, "scales must be float16 [K/group_size, N]")
     _require(A.dim() == 2, "Inputs must be 2D")
     _require(epilogue in ("none", "silu_mul"), "epilogue must be 'none' or 'silu_mul'")
+    _require(float(in_scale) == 1.0 or epilogue == "silu_mul", "in_scale is only used by the silu_mul epilogue")
     _require(out_dtype in (torch.float32, torch.float16), "out_dtype must be float32 or float16")
     N = scales.size(1)
     K, N = _qshape(qweight, N)
@@ -151,7 +153,7 @@ def matmul_w4a16(A: torch.Tensor, qweight: torch.Tensor, scales: torch.Tensor, g
             ws = _workspace(dev, need, zero_init=True)
             ws_ptr, ws_bytes = ws.data_ptr(), ws.numel()
         rc = lib.wmma_ops_w4a16_gemm_ex(A.data_ptr(), qweight.data_ptr(), scales.data_ptr(), C.data_ptr(), M, N, K,
-                                        group_size, split_k, mode, float(alpha), ws_ptr, ws_bytes,
+                                        group_size, split_k, mode, float(alpha), float(in_scale), ws_ptr, ws_bytes,
                                         _status_word(dev).data_ptr(), _stream(dev))
         _lib.check(rc)
         _post(dev)

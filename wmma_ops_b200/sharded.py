@@ -99,8 +99,8 @@ class ShardedDecoderLinears:
         # into its symmetric buffers and the sum is done through the NVSwitch by the library's own
         # kernel; forward() then returns views of those buffers (valid until the next forward)
         self.switch = switch if world > 1 else None
-        if self.switch is not None and reduce_dtype != torch.float16:
-            raise ValueError("the NVSwitch all-reduce sums fp16 buffers: use reduce_dtype=torch.float16")
+        if self.switch is not None and reduce_dtype != self.switch.partial_dtype:
+            raise ValueError("reduce_dtype must be the dtype of the switch's partial-output buffers")
         self.group = group
         self.reduce_dtype = reduce_dtype
         self.chunks = max(1, chunks)
@@ -174,12 +174,14 @@ class ShardedDecoderLinears:
         qkv16 = self._w4(x, "qkv", out_dtype=torch.float16, alpha=GLUE_SCALE)
         o_in = qkv16[:, :self.q_cols].contiguous()
         if self.switch is not None:
+            # partial outputs (fp16, or the fp32 accumulators) go straight into symmetric memory and are
+            # summed through the switch by one launch; the sums are fp16, so the 1/4 scaling of the MLP
+            # input is exact and is folded into the gate/up GEMM instead of a pass over the tensor
             T = x.shape[0]
-            self._w4(o_in, "o", out_dtype=torch.float16, out=self.switch.buffer(0, T))
+            self._w4(o_in, "o", out_dtype=out_dt, out=self.switch.buffer(0, T))
             attn_out = self.switch.reduce(0, T)
-            h = (attn_out * GLUE_SCALE).to(torch.float16)
-            act = self._w4(h, "gate_up", epilogue="silu_mul", alpha=GLUE_SCALE)
-            self._w4(act, "down", out_dtype=torch.float16, out=self.switch.buffer(1, T))
+            act = self._w4(attn_out, "gate_up", epilogue="silu_mul", alpha=GLUE_SCALE, in_scale=GLUE_SCALE)
+            self._w4(act, "down", out_dtype=out_dt, out=self.switch.buffer(1, T))
             mlp_out = self.switch.reduce(1, T)
             return attn_out, mlp_out
         self._matmul = lambda a, name: self._w4(a, name, out_dtype=out_dt)  # noqa: E731
@@ -203,7 +205,7 @@ class ShardedDecoderLinears:
         if getattr(self, "_streams", None) is None:
             self._streams = [torch.cuda.Stream(device=x.device) for _ in range(2)]
         if self.switch is not None:
-            attn_out, mlp_out = self.switch.buffer(0, T), self.switch.buffer(1, T)   # summed in place
+            attn_out = mlp_out = None   # views of the summed buffers, taken from the last chunk's reduce
         else:
             attn_out = torch.empty((T, self.packed["o"][1].shape[1]), dtype=out_dt, device=x.device)
             mlp_out = torch.empty_like(attn_out)
@@ -218,7 +220,7 @@ class ShardedDecoderLinears:
                     # partial output into the symmetric buffer, summed through the switch by the
                     # library's kernel on this side stream (a few CTAs; the other stream's GEMM
                     # keeps the remaining SMs busy)
-                    self._w4(o_in, "o", out_dtype=torch.float16, out=self.switch.buffer(0)[a:b])
+                    self._w4(o_in, "o", out_dtype=out_dt, out=self.switch.buffer(0)[a:b])
                     part = self.switch.reduce(0, b - a, row0=a, channel=c % 2)
                     work = None
                 else:
@@ -232,10 +234,14 @@ class ShardedDecoderLinears:
                 if work is not None:
                     work.wait()
                     attn_out[a:b].copy_(part)
-                h = (part * GLUE_SCALE).to(torch.float16)
-                act = self._w4(h, "gate_up", epilogue="silu_mul", alpha=GLUE_SCALE)
                 if self.switch is not None:
-                    self._w4(act, "down", out_dtype=torch.float16, out=self.switch.buffer(1)[a:b])
+                    h = part       # fp16 sums: the 1/4 scaling is exact and rides in the gate/up GEMM
+                    act = self._w4(h, "gate_up", epilogue="silu_mul", alpha=GLUE_SCALE, in_scale=GLUE_SCALE)
+                else:
+                    h = (part * GLUE_SCALE).to(torch.float16)
+                    act = self._w4(h, "gate_up", epilogue="silu_mul", alpha=GLUE_SCALE)
+                if self.switch is not None:
+                    self._w4(act, "down", out_dtype=out_dt, out=self.switch.buffer(1)[a:b])
                     part2 = self.switch.reduce(1, b - a, row0=a, channel=2 + c % 2)
                     work2 = None
                 else:
@@ -255,6 +261,8 @@ class ShardedDecoderLinears:
         # (which now depends on them) may still be using them
         if self.switch is None:
             keep += [p for p, _ in stage1] + [p for p, _ in stage2]
+        else:
+            attn_out, mlp_out = self.switch.summed(0, T), self.switch.summed(1, T)
         for t in keep:
             t.record_stream(main)
         return attn_out, mlp_out

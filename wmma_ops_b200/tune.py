@@ -105,9 +105,14 @@ def load_table(path) -> dict:
     return table
 
 
+_env_done = False
+
+
 def install_table(table: Optional[dict]) -> int:
     """Hands the table's GEMM entries to the library (None or an empty table removes the installed
     one). Returns the number of rows installed. Needs no GPU."""
+    global _env_done
+    _env_done = True   # an explicit installation is not replaced by the automatic one later
     lib = _lib.load()
     rows: List[int] = []
     if table:
@@ -119,9 +124,6 @@ def install_table(table: Optional[dict]) -> int:
     return len(rows) // 6
 
 
-_env_done = False
-
-
 DEFAULT_TABLE = os.path.join(os.path.dirname(os.path.abspath(__file__)), "tile_table_b200.json")
 
 
@@ -130,10 +132,8 @@ def install_from_env(force: bool = False) -> Optional[str]:
     unset, the table measured on B200 that ships with the package (its rows only match devices with
     the SM count they were measured on); "none" installs nothing. Called by the host layer before
     its first adaptive launch. Returns the path used, or None."""
-    global _env_done
     if _env_done and not force:
         return None
-    _env_done = True
     path = os.environ.get(ENV_VAR, "")
     if path.lower() == "none":
         install_table(None)
