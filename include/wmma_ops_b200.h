@@ -224,6 +224,16 @@ int wmma_ops_switch_allreduce(const void* mc_in, void* mc_out, size_t n_values, 
 int wmma_ops_fmha_fwd(const void* Q, const void* K, const void* V, void* O, int B, int H, int S,
                       int D, float scale, int causal, int* status, void* stream);
 
+/* The same attention for decode shapes: Sq <= 16 query rows per (b,h) against Skv >= Sq keys and
+ * values (Q, O [B,H,Sq,D]; K, V [B,H,Skv,D]; fp16, contiguous). With causal != 0 query row i sees
+ * the keys 0 .. Skv - Sq + i. The key range is cut into splits over the SMs; with more than one
+ * split the partial results go through `workspace` (wmma_ops_fmha_decode_workspace_bytes, any
+ * contents) and are merged in split order by a second launch on the same stream. Extends the
+ * signature of README.md:221-251 to a key/value cache; no counterpart in the reference tree. */
+size_t wmma_ops_fmha_decode_workspace_bytes(int B, int H, int Sq, int Skv, int D);
+int wmma_ops_fmha_decode(const void* Q, const void* K, const void* V, void* O, int B, int H, int Sq, int Skv, int D,
+                         float scale, int causal, void* workspace, size_t workspace_bytes, int* status, void* stream);
+
 /* On-disk container for prepacked INT4 weights (written and read by wmma_ops_b200/w4file.py; no
  * counterpart in the reference, which has no INT4 code). Little endian; every payload starts on a
  * 256-byte boundary, so a file mapped at a page boundary can be copied to the device block by

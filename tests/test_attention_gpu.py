@@ -117,6 +117,52 @@ def test_config4_causal_long_sequences_against_oracle(cuda, S):
             assert (got.cpu() - ref.float()).abs().max().item() < ABS_TOL
 
 
+# ---- decode shapes: a few query rows against a longer key/value sequence --------------------------
+
+def _seeded_decode(B, H, Sq, Skv, D, seed):
+    g = torch.Generator().manual_seed(seed)
+    mk = lambda S: torch.randn(B, H, S, D, generator=g, dtype=torch.float32).to(torch.float16)  # noqa: E731
+    return mk(Sq), mk(Skv), mk(Skv)
+
+
+@pytest.mark.parametrize("causal", [False, True])
+@pytest.mark.parametrize("shape", [(1, 2, 1, 1, 128), (1, 2, 1, 300, 128), (2, 3, 4, 1000, 64), (1, 4, 16, 4096, 128),
+                                   (1, 2, 16, 16, 128), (2, 2, 7, 37, 128), (1, 1, 3, 257, 64), (3, 5, 9, 2050, 128)])
+def test_decode_shapes_against_oracle(cuda, shape, causal):
+    B, H, Sq, Skv, D = shape
+    Q, K, V = _seeded_decode(B, H, Sq, Skv, D, seed=90 + Sq)
+    O = w.flash_attention(Q.to(cuda), K.to(cuda), V.to(cuda), causal=causal)
+    torch.cuda.synchronize()
+    w.check_status()
+    assert O.dtype == torch.float16 and O.shape == Q.shape
+    ref = oa.attention_ref(Q, K, V, causal)        # the causal mask lets row i see keys 0 .. Skv - Sq + i
+    assert og.rel_frobenius(O.float(), ref.float()) < REL_TOL
+    assert (O.cpu().float() - ref.float()).abs().max().item() < ABS_TOL
+
+
+def test_decode_config_shape_sampled_heads(cuda):
+    # B=4, H=32, one new token against 4096 cached keys: the oracle on a sample of (batch, head) pairs
+    Q, K, V = _seeded_decode(4, 32, 1, 4096, 128, seed=97)
+    O = w.flash_attention(Q.to(cuda), K.to(cuda), V.to(cuda), causal=True)
+    O2 = w.flash_attention(Q.to(cuda), K.to(cuda), V.to(cuda), causal=True)
+    torch.cuda.synchronize()
+    w.check_status()
+    assert torch.equal(O, O2)            # splits are merged in a fixed order
+    for b, h in [(0, 0), (2, 17), (3, 31)]:
+        ref = oa.attention_ref(Q[b:b + 1, h:h + 1], K[b:b + 1, h:h + 1], V[b:b + 1, h:h + 1], True)
+        assert og.rel_frobenius(O[b:b + 1, h:h + 1].float(), ref.float()) < REL_TOL
+
+
+def test_decode_rows_equal_the_last_rows_of_prefill(cuda):
+    # the last four query rows of a causal prefill see exactly what a four-row decode call sees
+    Q, K, V = oa.seeded_qkv(2, 3, 384, 128, seed=98)
+    full = w.flash_attention(Q.to(cuda), K.to(cuda), V.to(cuda), causal=True)
+    last = w.flash_attention(Q[:, :, -4:].contiguous().to(cuda), K.to(cuda), V.to(cuda), causal=True)
+    torch.cuda.synchronize()
+    w.check_status()
+    assert (full[:, :, -4:].float() - last.float()).abs().max().item() < 2e-3
+
+
 def test_errors(cuda):
     Q = torch.randn(1, 2, 64, 128, device=cuda).half()
     with pytest.raises(RuntimeError, match="Inputs must be float16"):
@@ -127,4 +173,8 @@ def test_errors(cuda):
         w.flash_attention(Q[..., :32].contiguous(), Q[..., :32].contiguous(), Q[..., :32].contiguous())
     with pytest.raises(RuntimeError, match="CUDA tensors"):
         w.flash_attention(Q.cpu(), Q, Q)
+    with pytest.raises(RuntimeError, match="may be longer than Q"):
+        w.flash_attention(Q, torch.cat([Q, Q], dim=2), torch.cat([Q, Q], dim=2))      # 64 query rows against 128 keys
+    with pytest.raises(RuntimeError, match="may be longer than Q"):
+        w.flash_attention(torch.cat([Q, Q], dim=2)[:, :, :8].contiguous(), Q[:, :, :4].contiguous(), Q[:, :, :4].contiguous())
     assert w.flash_attention(Q[:, :0], Q[:, :0], Q[:, :0]).shape == (1, 0, 64, 128)

@@ -51,7 +51,7 @@ def _free_port():
         return s.getsockname()[1]
 
 
-def _rank_main(rank, world, port, hidden, qkv_out, ffn, tokens, chunks, result):
+def _rank_main(rank, world, port, hidden, qkv_out, ffn, tokens, chunks, result, seq_len=None):
     os.environ["MASTER_ADDR"] = "127.0.0.1"
     os.environ["MASTER_PORT"] = str(port)
     dist.init_process_group("gloo", rank=rank, world_size=world)
@@ -62,11 +62,14 @@ def _rank_main(rank, world, port, hidden, qkv_out, ffn, tokens, chunks, result):
         local = sharded.shard_layer_weights(weights, rank, world, shapes)
         g = torch.Generator().manual_seed(5)
         x = torch.randn(tokens, hidden, generator=g).to(torch.float16)
+        from oracle import attention as oattn
         layer = sharded.ShardedDecoderLinears(
             local, world=world, group=128, chunks=chunks,
-            matmul=lambda a, name: int4.w4a16_ref(a, local[name][0], local[name][1], 128))
+            matmul=lambda a, name: int4.w4a16_ref(a, local[name][0], local[name][1], 128),
+            attention=None if seq_len is None else (seq_len, True),
+            attention_fn=lambda q, k, v, causal: oattn.attention_ref(q, k, v, causal))
         attn, mlp = layer(x)
-        ref_attn, ref_mlp = olayer.layer_ref(x, weights, 128)
+        ref_attn, ref_mlp = olayer.layer_ref(x, weights, 128, seq_len=seq_len, causal=True)
         e1 = ((attn - ref_attn).norm() / ref_attn.norm()).item()
         e2 = ((mlp - ref_mlp).norm() / ref_mlp.norm()).item()
         result[rank] = (e1, e2)
@@ -91,4 +94,24 @@ def test_sharded_layer_gloo(world, chunks):
         for r in range(world):
             e1, e2 = result[r]
             # sums of fp32 partials in a different order + one more fp16 rounding of activations
+            assert e1 < 1e-3 and e2 < 2e-3, (r, e1, e2)
+
+
+def test_sharded_layer_with_attention_gloo():
+    # heads are cut by rank with the Q, K and V sections (3 heads of 128 on 3 ranks, one each): the
+    # attention core between QKV and O needs no exchange and the result equals the unsharded oracle
+    world = 3
+    ctx = mp.get_context("spawn")
+    with ctx.Manager() as mgr:
+        result = mgr.dict()
+        port = _free_port()
+        procs = [ctx.Process(target=_rank_main, args=(r, world, port, 384, 1152, 768, 512, 1, result, 128))
+                 for r in range(world)]
+        for p in procs:
+            p.start()
+        for p in procs:
+            p.join(240)
+            assert p.exitcode == 0
+        for r in range(world):
+            e1, e2 = result[r]
             assert e1 < 1e-3 and e2 < 2e-3, (r, e1, e2)

@@ -57,6 +57,9 @@ SIGNATURES = {
                                         _c_float, _vp, _c_size_t, _vp, _vp]),
     "wmma_ops_fmha_fwd": (_c_int, [_vp, _vp, _vp, _vp, _c_int, _c_int, _c_int, _c_int, _c_float, _c_int,
                                    _vp, _vp]),
+    "wmma_ops_fmha_decode_workspace_bytes": (_c_size_t, [_c_int, _c_int, _c_int, _c_int, _c_int]),
+    "wmma_ops_fmha_decode": (_c_int, [_vp, _vp, _vp, _vp, _c_int, _c_int, _c_int, _c_int, _c_int, _c_float, _c_int, _vp,
+                                      _c_size_t, _vp, _vp]),
     "wmma_ops_multimem_allreduce_f16": (_c_int, [_vp, _c_size_t, _c_int, _c_int, _c_int, _vp]),
     "wmma_ops_switch_allreduce_flag_bytes": (_c_size_t, []),
     "wmma_ops_switch_allreduce": (_c_int, [_vp, _vp, _c_size_t, _c_int, _c_int, _c_int, _vp, _c_int, _c_int, _vp, _vp]),

@@ -1,12 +1,19 @@
 """flash_attention: the signature the reference documents (README.md:221-251),
 flash_attention(Q, K, V, causal=False, scale=-1.0) with Q, K, V [B, H, N, D] fp16 on one CUDA
-device and scale < 0 meaning 1/sqrt(D). Returns O with Q's shape and dtype."""
+device and scale < 0 meaning 1/sqrt(D). Returns O with Q's shape and dtype.
+
+Decode shapes: K and V may hold more rows than Q when Q has at most 16 (a few new tokens against a
+cache of keys and values, Q [B, H, Nq, D], K and V [B, H, Nkv, D], Nkv >= Nq). The causal mask then
+lets query row i see the keys up to Nkv - Nq + i. These calls, and any call with Nq <= 16, run on a
+kernel that splits the key range over the SMs instead of giving one CTA 128 query rows."""
 from __future__ import annotations
 
 import torch
 
 from . import _lib
-from .ops import _device_guard, _post, _require, _status_word, _stream
+from .ops import _device_guard, _post, _require, _status_word, _stream, _workspace
+
+DECODE_MAX_QUERIES = 16
 
 
 def flash_attention(Q: torch.Tensor, K: torch.Tensor, V: torch.Tensor, causal: bool = False,
@@ -17,17 +24,30 @@ def flash_attention(Q: torch.Tensor, K: torch.Tensor, V: torch.Tensor, causal: b
     _require(Q.dtype == torch.float16 and K.dtype == torch.float16 and V.dtype == torch.float16,
              "Inputs must be float16")
     _require(Q.dim() == 4 and K.dim() == 4 and V.dim() == 4, "Inputs must be 4D [B, H, N, D]")
-    _require(K.shape == Q.shape and V.shape == Q.shape, "Q, K and V must have the same shape")
+    _require(K.shape == V.shape, "K and V must have the same shape")
     B, H, S, D = Q.shape
+    Skv = K.size(2)
+    _require(K.size(0) == B and K.size(1) == H and K.size(3) == D and (Skv == S or (S <= DECODE_MAX_QUERIES and Skv >= S)),
+             "Q, K and V must have the same shape (K and V may be longer than Q when Q has at most 16 rows)")
     _require(D in (64, 128), f"head dimension must be 64 or 128 (got {D})")
     Q, K, V = Q.contiguous(), K.contiguous(), V.contiguous()
     O = torch.empty_like(Q)
     if Q.numel() == 0:
         return O
     dev = Q.device
+    lib = _lib.load()
     with _device_guard(dev):
-        rc = _lib.load().wmma_ops_fmha_fwd(Q.data_ptr(), K.data_ptr(), V.data_ptr(), O.data_ptr(), B, H, S, D,
-                                           float(scale), 1 if causal else 0, _status_word(dev).data_ptr(), _stream(dev))
+        if S <= DECODE_MAX_QUERIES and Skv >= 1:
+            need = lib.wmma_ops_fmha_decode_workspace_bytes(B, H, S, Skv, D)
+            ws_ptr, ws_bytes = None, 0
+            if need > 0:
+                ws = _workspace(dev, need)
+                ws_ptr, ws_bytes = ws.data_ptr(), ws.numel()
+            rc = lib.wmma_ops_fmha_decode(Q.data_ptr(), K.data_ptr(), V.data_ptr(), O.data_ptr(), B, H, S, Skv, D, float(scale),
+                                          1 if causal else 0, ws_ptr, ws_bytes, _status_word(dev).data_ptr(), _stream(dev))
+        else:
+            rc = lib.wmma_ops_fmha_fwd(Q.data_ptr(), K.data_ptr(), V.data_ptr(), O.data_ptr(), B, H, S, D,
+                                       float(scale), 1 if causal else 0, _status_word(dev).data_ptr(), _stream(dev))
         _lib.check(rc)
         _post(dev)
     return O

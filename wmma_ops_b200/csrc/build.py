@@ -25,6 +25,7 @@ SOURCES = [
     "w4a16_sm100.cu",
     "w4a16_decode_sm100.cu",
     "fmha_fwd_sm100.cu",
+    "fmha_decode_sm100.cu",
     "allreduce_sm100.cu",
     "selftest_sm100.cu",
 ]

@@ -27,7 +27,10 @@ namespace wb {
 constexpr int BM = 128;
 constexpr int BK = 64;
 constexpr int GEMM_THREADS = 192;
-constexpr int RASTER_GROUP_M = 16;  // m-blocks walked together so a wave reuses A and B in L2
+#ifndef WB_RASTER_GROUP_M
+#define WB_RASTER_GROUP_M 16
+#endif
+constexpr int RASTER_GROUP_M = WB_RASTER_GROUP_M;  // m-blocks walked together so a wave reuses A and B in L2
 
 template <int BN>
 struct GemmCfg {
@@ -248,7 +251,10 @@ gemm_f16f32_kernel(const __grid_constant__ CUtensorMap tmap_a,
                                 v.z += beta * cin.z;
                                 v.w += beta * cin.w;
                             }
-                            *reinterpret_cast<float4*>(out_row + col) = v;
+                            // split-K partials are read back by the reduce kernel: keep them in the L2;
+                            // final outputs stream out
+                            if (p.split_k > 1) *reinterpret_cast<float4*>(out_row + col) = v;
+                            else __stcs(reinterpret_cast<float4*>(out_row + col), v);
                         }
                     }
                 }
@@ -277,8 +283,14 @@ gemm_f16f32_kernel(const __grid_constant__ CUtensorMap tmap_a,
 // the leader's barrier); the leader's MMA thread commits to empty[] and acc_full[] of both CTAs
 // (one commit per CTA); both CTAs' epilogue threads arrive on the leader's acc_empty[] (256).
 constexpr int PAIR_BN = 256;
-constexpr int PAIR_KH = 2;                           // 64-deep k-blocks per pipeline stage
-constexpr int PAIR_STAGES = 6 / PAIR_KH;
+#ifndef WB_PAIR_KH
+#define WB_PAIR_KH 2
+#endif
+#ifndef WB_PAIR_STAGES
+#define WB_PAIR_STAGES (6 / WB_PAIR_KH)
+#endif
+constexpr int PAIR_KH = WB_PAIR_KH;                  // 64-deep k-blocks per pipeline stage
+constexpr int PAIR_STAGES = WB_PAIR_STAGES;
 constexpr int PAIR_A_BYTES = BM * BK * 2;            // 16 KB: this CTA's 128 rows of one k-block
 constexpr int PAIR_B_BYTES = 2 * BK * 64 * 2;        // 16 KB: this CTA's 128 columns (two boxes) of one k-block
 constexpr int PAIR_KB_BYTES = PAIR_A_BYTES + PAIR_B_BYTES;
@@ -465,7 +477,9 @@ gemm_f16f32_pair_kernel(const __grid_constant__ CUtensorMap tmap_a,
                                 v.z += beta * cin.z;
                                 v.w += beta * cin.w;
                             }
-                            *reinterpret_cast<float4*>(out_row + col) = v;
+                            // written once and never read by this kernel: a streaming store, so that
+                            // 256 MB of output do not push the operands out of the L2
+                            __stcs(reinterpret_cast<float4*>(out_row + col), v);
                         }
                     }
                 }

@@ -93,8 +93,16 @@ class ShardedDecoderLinears:
 
     def __init__(self, local_weights: Dict[str, Tuple[torch.Tensor, torch.Tensor]], world: int = 1,
                  group: int = GROUP, matmul: Optional[Callable] = None, all_reduce: Optional[Callable] = None,
-                 reduce_dtype: torch.dtype = torch.float32, chunks: int = 1, switch=None):
+                 reduce_dtype: torch.dtype = torch.float32, chunks: int = 1, switch=None,
+                 attention: Optional[Tuple[int, bool]] = None, head_dim: int = 128,
+                 attention_fn: Optional[Callable] = None):
         self.world = world
+        # (seq_len, causal): run the attention core between QKV and O on this rank's heads (the Q, K
+        # and V sections are cut by rank, so a rank holds whole heads and attention needs no exchange);
+        # None keeps the linears-only workload, where O's input is the rank's slice of the Q section
+        self.attention = attention
+        self.head_dim = head_dim
+        self._attention_fn = attention_fn    # (Q, K, V, causal) -> O on [batch, heads, seq, D]; default flash_attention
         # optional collective.SwitchAllReduce: the row-parallel GEMMs then write fp16 partial outputs
         # into its symmetric buffers and the sum is done through the NVSwitch by the library's own
         # kernel; forward() then returns views of those buffers (valid until the next forward)
@@ -148,6 +156,24 @@ class ShardedDecoderLinears:
                 h.wait()
         return parts[0] if n_chunks == 1 else torch.cat(parts, dim=0)
 
+    def _o_input(self, qkv16: torch.Tensor) -> torch.Tensor:
+        """O's input from this rank's fp16 QKV output [T, 3 * q_cols] (columns Q | K | V)."""
+        if self.attention is None:
+            return qkv16[:, :self.q_cols].contiguous()
+        fn = self._attention_fn
+        if fn is None:
+            from .attention import flash_attention as fn
+        seq_len, causal = self.attention
+        T = qkv16.shape[0]
+        heads = self.q_cols // self.head_dim
+        if T % seq_len != 0 or heads * self.head_dim != self.q_cols:
+            raise ValueError(f"{T} tokens are not whole sequences of {seq_len}, or the shard does not hold whole heads")
+        batch = T // seq_len
+        # [T, 3, heads, D] -> [3, batch, heads, seq, D]: the layout flash_attention takes
+        qkv = qkv16.view(batch, seq_len, 3, heads, self.head_dim).permute(2, 0, 3, 1, 4).contiguous()
+        o = fn(qkv[0], qkv[1], qkv[2], causal)
+        return o.permute(0, 2, 1, 3).reshape(T, self.q_cols)     # a copy: [batch, seq, heads, D] row-major
+
     def forward(self, x: torch.Tensor) -> Tuple[torch.Tensor, torch.Tensor]:
         """x fp16 [T, hidden] (replicated) -> (attn_out, mlp_out), both [T, hidden], replicated,
         in reduce_dtype. The glue is the oracle's: O's input is this rank's slice of the Q section
@@ -155,7 +181,10 @@ class ShardedDecoderLinears:
         if self.fused:
             return self._forward_fused(x)
         qkv = self._matmul(x, "qkv")
-        o_in = (qkv[:, :self.q_cols] * GLUE_SCALE).to(torch.float16)
+        if self.attention is None:
+            o_in = (qkv[:, :self.q_cols] * GLUE_SCALE).to(torch.float16)
+        else:
+            o_in = self._o_input((qkv * GLUE_SCALE).to(torch.float16))
         attn_out = self._row_parallel(o_in, "o")
         h = (attn_out * GLUE_SCALE).to(torch.float16)
         gu = self._matmul(h, "gate_up")
@@ -168,11 +197,12 @@ class ShardedDecoderLinears:
         """Same arithmetic with the glue inside the GEMM epilogues: QKV writes half(GLUE_SCALE * acc),
         gate/up writes half(GLUE_SCALE * silu(gate) * up); only the slice copy and the scaling of the
         all-reduced attention output remain as separate (small) kernels."""
-        if self.world > 1 and self.chunks > 1 and x.shape[0] >= 512 * self.chunks:
+        if self.world > 1 and self.chunks > 1 and x.shape[0] >= 512 * self.chunks and (
+                self.attention is None or (x.shape[0] // self.chunks) % self.attention[0] == 0):
             return self._forward_pipelined(x)
         out_dt = self.reduce_dtype
         qkv16 = self._w4(x, "qkv", out_dtype=torch.float16, alpha=GLUE_SCALE)
-        o_in = qkv16[:, :self.q_cols].contiguous()
+        o_in = self._o_input(qkv16)
         if self.switch is not None:
             # partial outputs (fp16, or the fp32 accumulators) go straight into symmetric memory and are
             # summed through the switch by one launch; the sums are fp16, so the 1/4 scaling of the MLP
@@ -215,7 +245,7 @@ class ShardedDecoderLinears:
         for c, (a, b) in enumerate(bounds):
             with torch.cuda.stream(self._streams[c % 2]):
                 qkv16 = self._w4(x[a:b], "qkv", out_dtype=torch.float16, alpha=GLUE_SCALE)
-                o_in = qkv16[:, :self.q_cols].contiguous()
+                o_in = self._o_input(qkv16)
                 if self.switch is not None:
                     # partial output into the symmetric buffer, summed through the switch by the
                     # library's kernel on this side stream (a few CTAs; the other stream's GEMM
