@@ -53,6 +53,22 @@ def test_static_scratch_matches_workspace_entry_point(cuda):
         _lib.check(rc)
         return out
 
+    # the property the entry point exists for: with the output preallocated, a call takes no device
+    # memory from anybody (torch's allocator included) and the driver reports the same free memory
+    pre_out = torch.empty(M, N, dtype=torch.float32, device=cuda)
+    rc = lib.wmma_ops_gemm_f16f32_splitk_static(A.data_ptr(), B.data_ptr(), None, pre_out.data_ptr(), M, N, K, 1.0, 0.0,
+                                                _lib.TILE_128x64, split, status.data_ptr(), stream)   # first call: address look-up
+    _lib.check(rc)
+    torch.cuda.synchronize()
+    before = (torch.cuda.memory_allocated(cuda), torch.cuda.memory_reserved(cuda), torch.cuda.mem_get_info(cuda)[0])
+    for _ in range(3):
+        rc = lib.wmma_ops_gemm_f16f32_splitk_static(A.data_ptr(), B.data_ptr(), None, pre_out.data_ptr(), M, N, K, 1.0, 0.0,
+                                                    _lib.TILE_128x64, split, status.data_ptr(), stream)
+        _lib.check(rc)
+    torch.cuda.synchronize()
+    after = (torch.cuda.memory_allocated(cuda), torch.cuda.memory_reserved(cuda), torch.cuda.mem_get_info(cuda)[0])
+    assert after == before
+
     # two calls in a row with different operands: the second finds the first one's partials in the array
     for Bm, alpha, beta in ((B, 1.0, 0.0), (B2, 2.0, 0.5)):
         got = static_call(Bm, alpha, beta)
@@ -77,6 +93,17 @@ def test_static_scratch_auto_plan_and_limit(cuda):
     _lib.check(rc)
     torch.cuda.synchronize()
     assert _rel(out, A.float() @ B.float()) < TOL
+    # more slices asked for than there are 64-deep k-blocks: the size check sees the plan that will run
+    # (M = N = 512, K = 256 has 4 k-blocks: 4 slices = 4 MiB fit, the 32 asked for would not)
+    M2, K2 = 512, 256
+    A2 = (torch.randn(M2, K2, generator=g) * K2 ** -0.5).half().to(cuda)
+    B3 = torch.randn(K2, M2, generator=g).half().to(cuda)
+    out2 = torch.empty(M2, M2, dtype=torch.float32, device=cuda)
+    rc = lib.wmma_ops_gemm_f16f32_splitk_static(A2.data_ptr(), B3.data_ptr(), None, out2.data_ptr(), M2, M2, K2, 1.0, 0.0,
+                                                _lib.TILE_128x128, 32, None, stream)
+    _lib.check(rc)
+    torch.cuda.synchronize()
+    assert _rel(out2, A2.float() @ B3.float()) < TOL
     # 4 slices of 2048 x 2048 fp32 = 64 MiB > 8 MiB: refused before anything is launched
     rc = lib.wmma_ops_gemm_f16f32_splitk_static(None, None, None, None, 2048, 2048, 4096, 1.0, 0.0, _lib.TILE_128x128, 4,
                                                 None, None)

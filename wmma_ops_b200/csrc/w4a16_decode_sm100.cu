@@ -12,19 +12,23 @@
 //     no tail. When there are too few column groups for that (narrow outputs), a cluster of 2 or 4
 //     CTAs shares a column range, each CTA takes one part of K, and the parts are added through
 //     distributed shared memory in rank order.
-//   * All loads in flight at once. The 16 warps of a CTA take the k-blocks round-robin. Each warp
-//     owns a private ring of shared-memory slots, one segment per slot, filled by one bulk copy
-//     (cp.async.bulk) that its lane 0 issues; for K = 4096 the four segments of a warp fit the ring,
-//     so every byte the CTA will read is requested in the first microsecond.
+//   * Weights in flight from the first microsecond. The 16 warps of a CTA take the k-blocks
+//     round-robin. Each warp owns a private ring of shared-memory slots, one weight segment per slot,
+//     filled by one bulk copy (cp.async.bulk) that its lane 0 issues; for K = 4096 the four segments
+//     of a warp fit the ring, so every weight byte the CTA will read is requested at once.
+//   * Activations and scales staged once. The activations (one bulk copy per row) and the fp16
+//     scales (plain 8-byte loads issued before any bulk copy) of a K segment are staged in shared
+//     memory ahead of the weight requests; the segment is all of K when that fits beside the ring.
 //   * Expansion next to the MMA. A warp expands a segment in registers straight into
 //     mma.sync.m16n8k16 A fragments (the weights are the 16-row operand, the tokens the 8-column
 //     one): a code or'ed into the mantissa of a fp16 constant and one fp16 subtraction give the
 //     exact integer code - 8. The fp32 sum of each 64-deep block is then multiplied by the group's
 //     fp16 scale. The MMAs of a k-step are issued for several column groups back to back
 //     (independent accumulators), so that no warp waits on a chain of dependent MMAs. The legacy
-//     tensor pipe (mma.sync) is what bounds the kernel: one m16n8k16 takes 16-24 cycles of an SM
-//     sub-partition, so a variant that left half of the zero points to an extra constant-operand
-//     MMA chain (fewer ALU instructions, 5e-7 relative error) was slower, not faster.
+//     tensor pipe (mma.sync) is what bounds the k-loop: measured with per-warp cycle counters it
+//     costs about 23 cycles of an SM sub-partition per m16n8k16, with 8 or with 16 activation rows
+//     and whatever the integer work beside it (a variant that left half of the zero points to an
+//     extra constant-operand MMA chain, 5e-7 relative error, was slower, not faster).
 //   * The 16 warps' tiles are added in warp order in shared memory (deterministic), and the output
 //     stage (fp32, fp16 with alpha, or silu(gate) * up) writes the result.
 //
@@ -65,13 +69,6 @@ __device__ __forceinline__ void sc_expand_pairs(uint32_t w, uint32_t& lo, uint32
     lo = h2_bits(__hsub2(bits_h2(t0), bits_h2(0x64086408u)));
     hi = h2_bits(__hsub2(bits_h2(t1), bits_h2(0x54805480u)));
 }
-
-#ifdef SC_TIMELINE
-__device__ long long sc_timeline[148 * 16 * 8];
-#define SC_MARK(i) do { if (lane == 0) sc_timeline[(blockIdx.x * 16 + warp) * 8 + (i)] = clock64(); } while (0)
-#else
-#define SC_MARK(i) do { } while (0)
-#endif
 
 __device__ __forceinline__ void sc_report(int* status, int warp, int detail) {
     if (status != nullptr && atomicCAS(status, 0, 4) == 0) {
@@ -135,10 +132,6 @@ __global__ void __launch_bounds__(SC_THREADS, 1) w4a16_decode_kernel(const W4Par
     // let the next kernel of the stream start its prologue as SMs free up (it waits for this one to
     // complete before it reads anything this one writes)
     asm volatile("griddepcontrol.launch_dependents;");
-    SC_MARK(0);
-#ifdef SC_TIMELINE
-    if (lane == 0) sc_timeline[(blockIdx.x * 16 + warp) * 8 + 7] = static_cast<long long>(globaltimer_ns());
-#endif
 
     const int rank = pl.ksplit > 1 ? static_cast<int>(cluster_ctarank()) : 0;
     const int cluster = pl.ksplit > 1 ? static_cast<int>(blockIdx.x) / pl.ksplit : static_cast<int>(blockIdx.x);
@@ -163,7 +156,6 @@ __global__ void __launch_bounds__(SC_THREADS, 1) w4a16_decode_kernel(const W4Par
         fence_proxy_async_smem();
     }
     __syncthreads();
-    SC_MARK(1);
 
     // The next weight segment to request: chunk rq_v0 (its first unit), k-block index rq_i of this warp.
     int rq_v0 = u0, rq_i = 0, rq_slot = 0;
@@ -281,7 +273,6 @@ __global__ void __launch_bounds__(SC_THREADS, 1) w4a16_decode_kernel(const W4Par
         asm volatile("griddepcontrol.wait;" ::: "memory");
         stage(u0, nun_first, k0, seg_first_end, true, nothing, first_requests);
     }
-    SC_MARK(2);
 
     // this lane's activation words within a staged row: token g (and g + 8), k 16t .. 16t+15 of a
     // k-block; tokens past M read the last row (their MMA columns are never stored)
@@ -322,19 +313,11 @@ __global__ void __launch_bounds__(SC_THREADS, 1) w4a16_decode_kernel(const W4Par
 #pragma unroll 1
             for (; k0 + warp + SC_WARPS * i < ks1; ++i) {
                 const int kb = k0 + warp + SC_WARPS * i;
-#ifdef SC_TIMELINE
-                const long long tw0 = clock64();
-#endif
                 if (ok && !mbar_wait(bars + 8u * slot, phase)) {
                     sc_report(p.status, warp, i);
                     ok = false;
                 }
                 ok = __all_sync(0xffffffffu, ok);
-                if (i == 0 && v0 == u0) SC_MARK(3);
-#ifdef SC_TIMELINE
-                if (lane == 0 && i > 0) sc_timeline[(blockIdx.x * 16 + warp) * 8 + 6] += clock64() - tw0;
-                if (lane == 0 && i == 0) sc_timeline[(blockIdx.x * 16 + warp) * 8 + 6] = 0;
-#endif
                 if (ok) {
                     const uint2* sl = reinterpret_cast<const uint2*>(ring_ptr + slot * pl.slot_bytes);
                     const int grel = (p.group_shift >= 0 ? (kb >> p.group_shift) : (kb / p.group_kb)) - g_first;
@@ -415,7 +398,6 @@ __global__ void __launch_bounds__(SC_THREADS, 1) w4a16_decode_kernel(const W4Par
                 }
             }
         }
-        if (v0 == u0) SC_MARK(4);
 
         // ---- this warp's tile of the chunk: [token][column], tokens below M only
         if (pl.alias_red) __syncthreads();  // the tiles lie over the ring: every warp has read its last slot
@@ -497,7 +479,6 @@ __global__ void __launch_bounds__(SC_THREADS, 1) w4a16_decode_kernel(const W4Par
                 }
             }
         }
-        if (v0 == u0) SC_MARK(5);
         // the tiles and the CTA's sums may be overwritten by the next chunk (and read by rank 0 until here)
         if (pl.ksplit > 1) cluster_sync();
         else if (v0 + pl.upc < u1) __syncthreads();
@@ -685,11 +666,6 @@ extern "C" int wmma_ops_set_w4a16_overlap(int enable) {
     return WMMA_OPS_OK;
 }
 
-#ifdef SC_TIMELINE
-extern "C" int wmma_ops_debug_timeline(long long* host_out) {
-    return cudaMemcpyFromSymbol(host_out, wb::sc_timeline, sizeof(long long) * 148 * 16 * 8) == cudaSuccess ? 0 : 2;
-}
-#endif
 
 extern "C" int wmma_ops_w4a16_decode_plan(int M, int N, int K, int group_size, int out_mode, int num_sms, int* plan) {
     using namespace wb;

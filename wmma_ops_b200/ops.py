@@ -64,17 +64,14 @@ def _workspace(device: torch.device, nbytes: int, zero_init: bool = False) -> to
     One buffer per (device, stream): kernels on different streams may overlap on the GPU and must
     not share partial sums or arrival counters; calls on one stream are ordered and may. A buffer
     that has been handed out is never freed (a kernel still running, or a captured CUDA graph, may
-    hold its address): when a larger one is needed the old one is kept in the list. While the stream
-    is being captured the buffer cannot grow; make the first call of each shape before capture."""
+    hold its address): when a larger one is needed the old one is kept in the list. A buffer that is
+    first needed while its stream is being captured is allocated there and then (torch serves it
+    from the graph's memory pool; the reference kept here keeps it alive as long as the graph needs it)."""
     stream_id = torch.cuda.current_stream(device).cuda_stream
     key = (device.type, device.index, stream_id, zero_init)
     bufs = _workspaces.setdefault(key, [])
     if bufs and bufs[-1].numel() >= nbytes:
         return bufs[-1]
-    if torch.cuda.is_current_stream_capturing():
-        raise RuntimeError(
-            f"wmma_ops_b200: this call needs {nbytes} bytes of scratch but the stream is being captured and its "
-            "scratch buffer cannot grow now; run the same call once before the capture")
     size = max(nbytes, 1 << 20)
     t = torch.zeros(size, dtype=torch.uint8, device=device) if zero_init else torch.empty(
         size, dtype=torch.uint8, device=device)
