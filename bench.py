@@ -37,8 +37,8 @@ if str(ROOT) not in sys.path:
 
 GEMM_N = 8192
 # DRAM bytes (read + write) per 8192^3 launch of the dominant kernel, from one ncu capture
-# of the CTA-pair kernel (1.08 GB read + 0.25 GB written; summary kept under profiles/).
-NCU_TRAFFIC_BYTES = {"gemm_8192": 1.33e9}
+# of the CTA-pair kernel (1.09 GB read + 0.25 GB written; summary kept under profiles/).
+NCU_TRAFFIC_BYTES = {"gemm_8192": 1.34e9}
 
 
 # ----------------------------------------------------------------------------- helpers
@@ -685,6 +685,12 @@ def run_kernel_only(args, w, dev, A, B):
         Kt = torch.randn(4, 32, 2048, 128, generator=gen, device=dev).half()
         V = torch.randn(4, 32, 2048, 128, generator=gen, device=dev).half()
         fn = lambda: w.flash_attention(Q, Kt, V, causal=name.endswith("causal"))  # noqa: E731
+    elif name in ("fmha_decode_sq1", "fmha_decode_sq16"):
+        Sq = int(name.split("_sq")[1])
+        Q = torch.randn(4, 32, Sq, 128, generator=gen, device=dev).half()
+        Kt = torch.randn(4, 32, 4096, 128, generator=gen, device=dev).half()
+        V = torch.randn(4, 32, 4096, 128, generator=gen, device=dev).half()
+        fn = lambda: w.flash_attention(Q, Kt, V, causal=True)  # noqa: E731
     else:
         raise SystemExit(f"unknown --kernel-only {name}")
     for _ in range(4):

@@ -1,9 +1,10 @@
 """Worker for tests/test_sharded_multi_gpu.py: run under torch.distributed.run with one rank per
 GPU (NCCL). Every rank computes the sharded layer on 1024 tokens with full layer shapes; EVERY rank
 compares its own copy of the all-reduced outputs with the single-process CPU oracle (rank 0
-computes it and broadcasts it). The accuracy gate is the workload's: relative Frobenius error
-<= 1e-3 against the fp32 oracle for the variants that claim it; the fp16-partials variants are
-held to their measured error plus margin and the number is printed either way.
+computes it and broadcasts it). The accuracy gate is the workload's, for every variant: relative
+Frobenius error <= 1e-3 against the fp32 oracle (measured at 2 ranks: 5e-5 with fp32 sums, 3.0e-4 to
+3.6e-4 with fp16 partial outputs, 2.1e-4 with fp32 partials and fp16 sums); the number is printed
+either way.
 
 A failure on one rank is recorded, not raised: every rank still reaches the final collectives and
 releases its symmetric-memory buffers before the process group is destroyed, so that no rank exits
@@ -23,8 +24,8 @@ from oracle import gemm as og  # noqa: E402
 from oracle import layer as olayer  # noqa: E402
 from wmma_ops_b200 import sharded  # noqa: E402
 
-GATE = 1e-3          # the workload's tolerance (attn_out and mlp_out)
-FP16_PARTIALS = 2e-3  # partial outputs rounded to fp16 before the sum: measured below 1e-3 / 1.3e-3
+GATE = 1e-3           # the workload's tolerance (attn_out and mlp_out)
+FP16_PARTIALS = 1e-3  # partial outputs rounded to fp16 before the sum: measured 3.0e-4 .. 3.6e-4
 
 
 def main():

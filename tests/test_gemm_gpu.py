@@ -252,3 +252,31 @@ def test_matmul_host_pipelined_matches_device_matmul(cuda):
         assert torch.equal(o, outs[0]) and og.rel_frobenius(o, ref) < 1e-6
     with pytest.raises(RuntimeError, match="pinned"):
         w.matmul_host(A.clone(), B)
+
+
+def test_adaptive_is_near_the_best_fixed_tile(cuda):
+    # With the measured tile table installed (the one that ships with the package, or the one named by
+    # WMMA_OPS_TILE_TABLE), matmul_adaptive is within 5 % (plus 2 us of timing noise for the
+    # launch-bound small products) of the best fixed (tile, split_k) on every shape the reference tunes
+    # and reports on (autotune.py:64-82, benchmark_summary.py:10-19) and on the config shapes.
+    from wmma_ops_b200 import tune
+    from wmma_ops_b200.ops import _launch_gemm, select_tile
+    tune.install_from_env(force=True)
+    sms = torch.cuda.get_device_properties(cuda).multi_processor_count
+    worst = []
+    for (M, N, K) in tune.TUNE_SHAPES:
+        res = tune.measure_shape(M, N, K, cuda)
+        best_key = min(res, key=res.get)
+        tile, split = select_tile(M, N, K, sms)
+        chosen = res.get(f"{tile}:{split}")
+        if chosen is None:      # a split factor outside the candidate list: time it the same way
+            A, B = tune._operands(M, N, K, cuda, 1)[0]
+            C = torch.empty((M, N), dtype=torch.float32, device=cuda)
+            chosen = tune._time_us(lambda: _launch_gemm(A, B, None, C, M, N, K, 1.0, 0.0, tile, split), 20)
+        ratio = chosen / res[best_key]
+        print(f"{M}x{N}x{K}: adaptive {tune.TILE_NAMES[tile]}/{split} {chosen:.1f} us, best {best_key} {res[best_key]:.1f} us, x{ratio:.3f}")
+        if chosen > 1.05 * res[best_key] + 2.0:
+            worst.append((M, N, K, tile, split, chosen, best_key, res[best_key]))
+    torch.cuda.synchronize()
+    w.check_status()
+    assert not worst, worst

@@ -278,21 +278,21 @@ __global__ void __launch_bounds__(FD_THREADS) fmha_decode_kernel(const FdParams 
 // Merges the splits of one (batch, head) in split order: out = sum_s w_s O_s / sum_s w_s l_s, w_s = 2^(m_s - max m).
 template <int D>
 __global__ void __launch_bounds__(D) fmha_decode_merge_kernel(const FdParams p) {
-    const int bh = blockIdx.x, col = threadIdx.x;
-    for (int row = 0; row < p.Sq; ++row) {
-        const float* base = p.ws + (static_cast<size_t>(bh) * p.splits * p.Sq + row) * (D + 2);
-        const size_t stride = static_cast<size_t>(p.Sq) * (D + 2);
-        float mstar = -INFINITY;
-        for (int s = 0; s < p.splits; ++s) mstar = fmaxf(mstar, base[s * stride + D]);
-        const float ref = mstar == -INFINITY ? 0.f : mstar;
-        float acc = 0.f, l = 0.f;
-        for (int s = 0; s < p.splits; ++s) {
-            const float wgt = exp2f(base[s * stride + D] - ref);
-            acc += wgt * base[s * stride + col];
-            l += wgt * base[s * stride + D + 1];
-        }
-        p.O[(static_cast<size_t>(bh) * p.Sq + row) * D + col] = __float2half_rn(l > 0.f ? acc / l : 0.f);
+    // one CTA per (batch, head, query row), one thread per output column; all loads of a thread are
+    // issued before the first use (the maxima first, then every split's value and sum)
+    const int bh = blockIdx.x, row = blockIdx.y, col = threadIdx.x;
+    const float* base = p.ws + (static_cast<size_t>(bh) * p.splits * p.Sq + row) * (D + 2);
+    const size_t stride = static_cast<size_t>(p.Sq) * (D + 2);
+    float mstar = -INFINITY;
+    for (int s = 0; s < p.splits; ++s) mstar = fmaxf(mstar, base[s * stride + D]);
+    const float ref = mstar == -INFINITY ? 0.f : mstar;
+    float acc = 0.f, l = 0.f;
+    for (int s = 0; s < p.splits; ++s) {
+        const float wgt = exp2f(base[s * stride + D] - ref);
+        acc += wgt * base[s * stride + col];
+        l += wgt * base[s * stride + D + 1];
     }
+    p.O[(static_cast<size_t>(bh) * p.Sq + row) * D + col] = __float2half_rn(l > 0.f ? acc / l : 0.f);
 }
 
 static void fd_plan(int BH, int Skv, int sms, int* splits, int* keys_per_split) {
@@ -324,7 +324,7 @@ static int fd_launch(const FdParams& p, cudaStream_t stream) {
     fmha_decode_kernel<D><<<grid, FD_THREADS, SMEM, stream>>>(p);
     WB_CHECK_CUDA(cudaGetLastError());
     if (p.splits > 1) {
-        fmha_decode_merge_kernel<D><<<p.B * p.H, D, 0, stream>>>(p);
+        fmha_decode_merge_kernel<D><<<dim3(p.B * p.H, p.Sq), D, 0, stream>>>(p);
         WB_CHECK_CUDA(cudaGetLastError());
     }
     return WMMA_OPS_OK;
