@@ -425,17 +425,18 @@ def measure_layer(w, dev, rank, world, steps):
             except Exception as e:
                 out[label + "_cuda_graph"] = {"error": f"{type(e).__name__}: {str(e)[:200]}"}
             del layer
-            # two token chunks on two streams: the sum of one chunk (32 CTAs) runs beside the GEMMs of
-            # the other (the remaining SMs)
-            try:
-                sw.max_ctas = 32
-                w.set_sm_margin(32)
-                layer = sharded.ShardedDecoderLinears(local, world=world, reduce_dtype=part, switch=sw, chunks=2)
-                run, outs = graphed(layer)
-                record(label + "_2chunks_cuda_graph", run, outs)
-                del run, outs, layer
-            except Exception as e:
-                out[label + "_2chunks_cuda_graph"] = {"error": f"{type(e).__name__}: {str(e)[:200]}"}
+            # token chunks on two streams: the sum of one chunk (a few CTAs: its time does not depend on
+            # their number) runs beside the GEMMs of the next (the remaining SMs)
+            for chunks in (2, 4):
+                try:
+                    sw.max_ctas = 16
+                    w.set_sm_margin(16)
+                    layer = sharded.ShardedDecoderLinears(local, world=world, reduce_dtype=part, switch=sw, chunks=chunks)
+                    run, outs = graphed(layer)
+                    record(f"{label}_{chunks}chunks_cuda_graph", run, outs)
+                    del run, outs, layer
+                except Exception as e:
+                    out[f"{label}_{chunks}chunks_cuda_graph"] = {"error": f"{type(e).__name__}: {str(e)[:200]}"}
             sw.max_ctas = 0
             w.set_sm_margin(0)
             del sw
