@@ -166,6 +166,26 @@ def test_fused_silu_mul_output(cuda, M):
     assert og.rel_frobenius(out.float(), ref) < 2e-3    # fp16 output rounding + fast exp
 
 
+@pytest.mark.parametrize("M", [4, 16, 200])
+def test_fused_silu_mul_with_input_scale(cuda, M):
+    # in_scale stands for a scale of the activations that the caller left out: silu_mul(x, in_scale=s)
+    # equals silu_mul(s * x) when s is a power of two (the scaling of x is then exact)
+    K, F = 512, 256
+    codes, scales = int4.seeded_w4(K, 2 * F, 128, seed=17)
+    A, _ = og.seeded_ab(M, 8, K, seed=18)
+    ci, si = w.interleave_gate_up(codes.to(cuda), scales.to(cuda))
+    q, sc = w.int4_prepack(ci, si, 128)
+    folded = w.matmul_w4a16(A.to(cuda), q, sc, 128, epilogue="silu_mul", alpha=0.5, in_scale=0.25)
+    scaled = w.matmul_w4a16((A * 0.25).to(cuda), q, sc, 128, epilogue="silu_mul", alpha=0.5)
+    _sync_ok()
+    gu = int4.w4a16_ref(A * 0.25, codes, scales, 128)
+    ref = torch.nn.functional.silu(gu[:, :F]) * gu[:, F:] * 0.5
+    assert og.rel_frobenius(folded.float(), ref) < 2e-3
+    assert (folded.float() - scaled.float()).abs().max().item() <= 2 ** -9 * ref.abs().max().item()
+    with pytest.raises(RuntimeError, match="in_scale is only used"):
+        w.matmul_w4a16(A.to(cuda), q, sc, 128, in_scale=0.5)
+
+
 def test_w4a16_errors(cuda):
     codes, scales = int4.seeded_w4(256, 128, 128, seed=8)
     q, sc = w.int4_prepack(codes.to(cuda), scales.to(cuda), 128)
