@@ -372,6 +372,7 @@ def measure_layer(w, dev, rank, world, steps):
             ms = time_region(run, max(3, min(steps, 10)), world, dev)
             attn, mlp = outputs()
             torch.cuda.synchronize()
+            w.check_status(dev)      # a bounded wait that gave up is an error of the variant, not a timing
             errs = torch.tensor([og.rel_frobenius(attn[:sample].float().cpu(), refs[0].cpu()),
                                  og.rel_frobenius(mlp[:sample].float().cpu(), refs[1].cpu())], dtype=torch.float64, device=dev)
             if world > 1:
@@ -425,18 +426,26 @@ def measure_layer(w, dev, rank, world, steps):
             except Exception as e:
                 out[label + "_cuda_graph"] = {"error": f"{type(e).__name__}: {str(e)[:200]}"}
             del layer
-            # token chunks on two streams: the sum of one chunk (a few CTAs: its time does not depend on
-            # their number) runs beside the GEMMs of the next (the remaining SMs)
-            for chunks in (2, 4):
+            # token chunks on two streams: the sum of one chunk runs beside the GEMMs of the next. Either the
+            # GEMMs leave 16 SMs to the sum ("_16sms_for_the_sum"), or they take every SM and the sum's small
+            # CTAs run on the same SMs (the prefill kernel leaves them registers and shared memory)
+            for chunks, margin, ctas, follow, suffix in (
+                    (2, 16, 32, False, "_16sms_for_the_sum"), (4, 16, 32, False, "_16sms_for_the_sum"),
+                    (2, 0, 32, False, ""), (2, 0, 64, False, "_64ctas"), (4, 0, 32, False, ""),
+                    # "following": each sum runs beside the GEMM that produces its input, token block by token block
+                    (1, 0, 32, True, "_following"), (2, 0, 32, True, "_following"), (2, 0, 64, True, "_following_64ctas"),
+                    (2, 32, 32, True, "_following_32sms_for_the_sum")):
+                name = f"{label}_{chunks}chunks{suffix}_cuda_graph"
                 try:
-                    sw.max_ctas = 16
-                    w.set_sm_margin(16)
-                    layer = sharded.ShardedDecoderLinears(local, world=world, reduce_dtype=part, switch=sw, chunks=chunks)
+                    sw.max_ctas = ctas
+                    w.set_sm_margin(margin)
+                    layer = sharded.ShardedDecoderLinears(local, world=world, reduce_dtype=part, switch=sw, chunks=chunks,
+                                                          follow=follow)
                     run, outs = graphed(layer)
-                    record(f"{label}_{chunks}chunks_cuda_graph", run, outs)
+                    record(name, run, outs)
                     del run, outs, layer
                 except Exception as e:
-                    out[f"{label}_{chunks}chunks_cuda_graph"] = {"error": f"{type(e).__name__}: {str(e)[:200]}"}
+                    out[name] = {"error": f"{type(e).__name__}: {str(e)[:200]}"}
             sw.max_ctas = 0
             w.set_sm_margin(0)
             del sw

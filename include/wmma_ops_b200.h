@@ -187,6 +187,20 @@ int wmma_ops_w4a16_gemm_ex(const void* A, const void* qweight, const void* scale
                            int K, int group_size, int split_k, int out_mode, float alpha, float in_scale,
                            void* workspace, size_t workspace_bytes, int* status, void* stream);
 
+/* wmma_ops_w4a16_gemm_ex that tells a consumer how far it has got (no counterpart in the reference).
+ * M > 16, split_k 0 or 1. The output is produced token block by token block (blocks of
+ * wmma_ops_w4a16_token_block(M) rows, all column tiles of a block before the next block), and
+ * block_done[b] (device memory, zero before the call, one int per token block) is incremented, after a
+ * system-scope fence, each time one 128-column tile of block b has been written: block b is complete
+ * when block_done[b] == ceil(N_out / 128), N_out = N. A kernel that runs beside this one (the sum over
+ * the ranks, wmma_ops_switch_allreduce_following) can then consume the output while later blocks are
+ * still being computed. block_done may be NULL (then this is wmma_ops_w4a16_gemm_ex). */
+int wmma_ops_w4a16_gemm_blocks(const void* A, const void* qweight, const void* scales, void* C, int M, int N,
+                               int K, int group_size, int split_k, int out_mode, float alpha, float in_scale,
+                               void* workspace, size_t workspace_bytes, int* block_done, int* status,
+                               void* stream);
+int wmma_ops_w4a16_token_block(int M);
+
 /* Sum of an fp16 buffer over the ranks of one NVSwitch domain, in place, for the row-parallel
  * outputs of the sharded layer (no counterpart in the reference, which is single-GPU).
  * multicast_ptr is the NVLink multicast address of a buffer of n_halves fp16 values that every
@@ -208,7 +222,7 @@ int wmma_ops_multimem_allreduce_f16(void* multicast_ptr, size_t n_halves, int ra
  *                   zero-initialised symmetric buffer of wmma_ops_switch_allreduce_flag_bytes()
  *                   bytes that is used for nothing else.
  *   channel         0..3; calls that may be in flight at the same time need different channels.
- *   max_ctas        CTAs per rank (<= 0: 64); all ranks must pass the same value.
+ *   max_ctas        CTAs (of 192 threads) per rank (<= 0: 128); all ranks must pass the same value.
  * Every rank calls it with the same arguments on a stream on which its partial outputs have been
  * written; when the call has completed on a rank, that rank's copy of the output holds all sums.
  * A rank that does not arrive within about a second makes the others record {5, rank, block,
@@ -216,6 +230,23 @@ int wmma_ops_multimem_allreduce_f16(void* multicast_ptr, size_t n_halves, int ra
 size_t wmma_ops_switch_allreduce_flag_bytes(void);
 int wmma_ops_switch_allreduce(const void* mc_in, void* mc_out, size_t n_values, int in_is_f32, int rank, int world,
                               const void* flag_ptrs_dev, int channel, int max_ctas, int* status, void* stream);
+
+/* wmma_ops_switch_allreduce for a [rows, cols] buffer that a GEMM of this rank is still writing, on another
+ * stream, token block by token block (wmma_ops_w4a16_gemm_blocks): each block of block_rows rows is summed
+ * as soon as every rank's block_done[] entry for it has reached tiles_per_block, so the exchange runs beside
+ * the GEMM and only the last block's sum remains after it.
+ *   mc_in / mc_out  multicast addresses of the first of the `rows` rows (cols % 8 == 0), as above.
+ *   block_done      the counters given to the GEMM; seen: as many zero-initialised ints of device memory.
+ *                   Both are zero again when the call has completed.
+ *   max_ctas        <= 0: 32. Up to four CTAs share a token block when there are fewer blocks than CTAs.
+ * Launch the GEMM first and leave it room to become resident: either as many SMs free as this call has
+ * CTAs (wmma_ops_set_sm_margin), or a product with more than 128 rows, whose kernel leaves room for one
+ * CTA of this one on every SM. A CTA whose GEMM does not finish a block within about a second records
+ * {6, rank, CTA, token block} in `status` and carries on. */
+int wmma_ops_switch_allreduce_following(const void* mc_in, void* mc_out, int rows, int cols, int in_is_f32,
+                                        int block_rows, int* block_done, int* seen, int tiles_per_block, int rank,
+                                        int world, const void* flag_ptrs_dev, int channel, int max_ctas, int* status,
+                                        void* stream);
 
 /* Flash-attention forward: O = softmax(scale * Q K^T [+ causal mask]) V per (b,h).
  * Q, K, V, O are [B,H,S,D] fp16 contiguous; the signature documented in the reference's

@@ -82,14 +82,24 @@ def main():
             if rank == 0:
                 print(f"switch all-reduce unavailable: {type(e).__name__}: {str(e)[:200]}", flush=True)
         if sw16 is not None:
-            for label, sw, rdt, chunks, tol in (("switch fp32 partials", sw32, torch.float32, 1, GATE),
-                                                ("switch fp16 partials", sw16, torch.float16, 1, FP16_PARTIALS),
-                                                ("switch fp16 partials, 2 chunks", sw16, torch.float16, 2, FP16_PARTIALS),
-                                                ("switch fp32 partials, 2 chunks", sw32, torch.float32, 2, GATE)):
-                if chunks > 1:
-                    sw.max_ctas = 32
-                    w.set_sm_margin(32)
-                layer = sharded.ShardedDecoderLinears(local, world=world, reduce_dtype=rdt, chunks=chunks, switch=sw)
+            # margin: SMs the GEMMs leave to the sum kernel; 0 = its CTAs share SMs with the prefill kernel
+            # margin: SMs the GEMMs leave to the sum kernel; 0 = its CTAs share SMs with the prefill kernel.
+            # follow: the sum runs beside the GEMM that produces its input, token block by token block
+            for label, sw, rdt, chunks, margin, follow, tol in (
+                    ("switch fp32 partials", sw32, torch.float32, 1, 0, False, GATE),
+                    ("switch fp16 partials", sw16, torch.float16, 1, 0, False, FP16_PARTIALS),
+                    ("switch fp16 partials, 2 chunks, 32 SMs left", sw16, torch.float16, 2, 32, False, FP16_PARTIALS),
+                    ("switch fp16 partials, 2 chunks, shared SMs", sw16, torch.float16, 2, 0, False, FP16_PARTIALS),
+                    ("switch fp32 partials, 2 chunks, shared SMs", sw32, torch.float32, 2, 0, False, GATE),
+                    ("switch fp16 partials, following, 32 SMs left", sw16, torch.float16, 1, 32, True, FP16_PARTIALS),
+                    ("switch fp16 partials, following, shared SMs", sw16, torch.float16, 1, 0, True, FP16_PARTIALS),
+                    ("switch fp32 partials, following, shared SMs", sw32, torch.float32, 1, 0, True, GATE),
+                    ("switch fp16 partials, 2 chunks, following, shared SMs", sw16, torch.float16, 2, 0, True,
+                     FP16_PARTIALS)):
+                sw.max_ctas = 32 if (chunks > 1 or follow) else 0
+                w.set_sm_margin(margin)
+                layer = sharded.ShardedDecoderLinears(local, world=world, reduce_dtype=rdt, chunks=chunks, switch=sw,
+                                                      follow=follow)
                 for _ in range(2):      # twice: the barrier epochs advance, nothing is reset between calls
                     ok = check(label, layer, tol, tol) and ok
                 layer = None

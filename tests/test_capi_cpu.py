@@ -186,3 +186,28 @@ def test_w4a16_decode_plan_choices(lib):
     assert lib.wmma_ops_w4a16_decode_plan(4, 128, 256, 96, 0, 148, out) == _lib.ERR_INVALID
     # plain setters
     assert lib.wmma_ops_set_w4a16_overlap(1) == 0 and lib.wmma_ops_set_w4a16_overlap(0) == 0
+
+
+def test_reset_hooks_follow_reset_workspaces():
+    """Objects that own device-side counters (the switch all-reduce) register for reset_workspaces: the call
+    reaches the objects of that device while they live, and no others."""
+    import torch
+    from wmma_ops_b200 import ops
+
+    class Owner:
+        def __init__(self, device):
+            self.device, self.resets = device, 0
+
+        def reset(self):
+            self.resets += 1
+
+    a, b = Owner(torch.device("cuda", 0)), Owner(torch.device("cuda", 1))
+    ops._register_reset(a)
+    ops._register_reset(b)
+    ops.reset_workspaces(torch.device("cuda", 0))
+    assert (a.resets, b.resets) == (1, 0)
+    ops.reset_workspaces("cuda:1")
+    assert (a.resets, b.resets) == (1, 1)
+    del a
+    ops.reset_workspaces(torch.device("cuda", 0))   # a dead owner is dropped silently
+    assert b.resets == 1

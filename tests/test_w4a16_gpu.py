@@ -336,3 +336,27 @@ def test_prepacked_weights_survive_the_file_format(cuda, tmp_path):
             b = w.matmul_w4a16(x[:M].contiguous(), q2, sc2, g2)
             _sync_ok()
             assert torch.equal(a, b)
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("M,N,K", [(300, 256, 256), (1024, 4096, 512), (700, 384, 1024)])
+def test_block_completion_counters(M, N, K):
+    """With block_done the kernel walks the rows block by block; the result is the same bit for bit and
+    every block's counter ends at the number of 128-column tiles."""
+    torch.manual_seed(M + N)
+    dev = torch.device("cuda", 0)
+    codes = torch.randint(0, 16, (K, N), dtype=torch.uint8, device=dev)
+    scales = (torch.rand((K // 128, N), device=dev) * 0.02 + 0.005).half()
+    q, scales = w.int4_prepack(codes, scales, 128)
+    x = (torch.randn((M, K), device=dev) * 0.5).half()
+    plain = w.matmul_w4a16(x, q, scales, 128, out_dtype=torch.float16)
+    bt = w.w4a16_token_block(M)
+    assert bt in (32, 64, 128, 256)
+    blocks = (M + bt - 1) // bt
+    done = torch.zeros(blocks, dtype=torch.int32, device=dev)
+    followed = w.matmul_w4a16(x, q, scales, 128, out_dtype=torch.float16, block_done=done)
+    w.check_status()
+    assert torch.equal(plain, followed)
+    assert done.tolist() == [(N + 127) // 128] * blocks
+    with pytest.raises(RuntimeError):
+        w.matmul_w4a16(x[:8], q, scales, 128, block_done=done)

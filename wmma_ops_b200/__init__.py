@@ -36,7 +36,7 @@ from .ops import (  # noqa: F401
 
 from .attention import flash_attention  # noqa: F401,E402
 from .quant import (int4_dequant, int4_prepack, int4_unpack, interleave_gate_up, matmul_w4a16,  # noqa: F401,E402
-                    set_w4a16_overlap)
+                    set_w4a16_overlap, w4a16_token_block)
 
 from .w4file import load_w4, read_w4_index, save_w4  # noqa: F401,E402
 

@@ -55,6 +55,9 @@ SIGNATURES = {
                                      _c_size_t, _vp, _vp]),
     "wmma_ops_w4a16_gemm_ex": (_c_int, [_vp, _vp, _vp, _vp, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_float,
                                         _c_float, _vp, _c_size_t, _vp, _vp]),
+    "wmma_ops_w4a16_gemm_blocks": (_c_int, [_vp, _vp, _vp, _vp, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_float,
+                                            _c_float, _vp, _c_size_t, _vp, _vp, _vp]),
+    "wmma_ops_w4a16_token_block": (_c_int, [_c_int]),
     "wmma_ops_fmha_fwd": (_c_int, [_vp, _vp, _vp, _vp, _c_int, _c_int, _c_int, _c_int, _c_float, _c_int,
                                    _vp, _vp]),
     "wmma_ops_fmha_decode_workspace_bytes": (_c_size_t, [_c_int, _c_int, _c_int, _c_int, _c_int]),
@@ -63,6 +66,8 @@ SIGNATURES = {
     "wmma_ops_multimem_allreduce_f16": (_c_int, [_vp, _c_size_t, _c_int, _c_int, _c_int, _vp]),
     "wmma_ops_switch_allreduce_flag_bytes": (_c_size_t, []),
     "wmma_ops_switch_allreduce": (_c_int, [_vp, _vp, _c_size_t, _c_int, _c_int, _c_int, _vp, _c_int, _c_int, _vp, _vp]),
+    "wmma_ops_switch_allreduce_following": (_c_int, [_vp, _vp, _c_int, _c_int, _c_int, _c_int, _vp, _vp, _c_int, _c_int, _c_int,
+                                                     _vp, _c_int, _c_int, _vp, _vp]),
     "wmma_ops_selftest_wait_expiry": (_c_int, [ctypes.c_longlong, _c_int, _vp, _vp]),
     "wmma_ops_selftest_debug_index": (_c_int, [_c_int, _c_int, _vp, _vp, _vp]),
     "wmma_ops_debug_checks_enabled": (_c_int, []),

@@ -22,7 +22,7 @@ from typing import List, Optional, Tuple
 import torch
 
 from . import _lib
-from .ops import _status_word
+from .ops import _register_reset, _status_word
 
 
 class SwitchAllReduce:
@@ -70,6 +70,10 @@ class SwitchAllReduce:
                 raise RuntimeError("SwitchAllReduce: this system gives no NVLink multicast address")
             self._partial.append((t, hdl))
             self._summed.append(shared((rows, cols), torch.float16) if partial_dtype == torch.float32 else (t, hdl))
+        # per slot: tile counters a GEMM advances per token block, and how many CTAs of the following sum
+        # have seen a block complete; both return to zero by themselves (see reduce_following)
+        self._blocks = torch.zeros((slots, 2, rows // 32 + 2), dtype=torch.int32, device=device)
+        _register_reset(self)
         torch.cuda.synchronize(device)
         dist.barrier(self.group)      # every rank's flags are zero before any peer writes to them
 
@@ -103,3 +107,37 @@ class SwitchAllReduce:
             self.world, self._flag_hdl.buffer_ptrs_dev, channel, self.max_ctas, _status_word(self.device).data_ptr(), stream)
         _lib.check(rc)
         return out[row0:row0 + rows]
+
+    def counters(self, slot: int, row0: int = 0) -> torch.Tensor:
+        """Tile counters for a GEMM that writes rows [row0, ...) of buffer `slot` and is to be followed by
+        reduce_following: pass them as matmul_w4a16(..., block_done=...)."""
+        if row0 % 32 != 0:
+            raise RuntimeError("SwitchAllReduce.counters: row0 must be a multiple of 32")
+        return self._blocks[slot, 0, row0 // 32:]
+
+    def reduce_following(self, slot: int, rows: int, token_block: int, tiles_per_block: int, row0: int = 0,
+                         channel: Optional[int] = None) -> torch.Tensor:
+        """reduce() for a buffer that a GEMM of this rank is still writing on ANOTHER stream, token block by
+        token block (matmul_w4a16 with block_done=counters(slot, row0)): on the current stream, sums each
+        block of `token_block` rows as soon as every rank's GEMM has counted `tiles_per_block` column tiles
+        for it. The caller launches the GEMM first, then this, and joins the two streams afterwards."""
+        part, phdl = self._partial[slot]
+        out, ohdl = self._summed[slot]
+        if row0 < 0 or rows < 1 or row0 + rows > self.rows or row0 % 32 != 0:
+            raise RuntimeError("SwitchAllReduce.reduce_following: row range outside the buffer or row0 not a multiple of 32")
+        channel = slot if channel is None else channel
+        stream = torch.cuda.current_stream(self.device).cuda_stream
+        f32 = self.partial_dtype == torch.float32
+        off = row0 * self.cols
+        done = self._blocks[slot, 0, row0 // 32:]
+        seen = self._blocks[slot, 1, row0 // 32:]
+        rc = self._lib.wmma_ops_switch_allreduce_following(
+            phdl.multicast_ptr + off * (4 if f32 else 2), ohdl.multicast_ptr + off * 2, rows, self.cols, 1 if f32 else 0,
+            token_block, done.data_ptr(), seen.data_ptr(), tiles_per_block, self.rank, self.world,
+            self._flag_hdl.buffer_ptrs_dev, channel, self.max_ctas, _status_word(self.device).data_ptr(), stream)
+        _lib.check(rc)
+        return out[row0:row0 + rows]
+
+    def reset(self) -> None:
+        """After a non-zero status word: the tile counters may have been left behind."""
+        self._blocks.zero_()

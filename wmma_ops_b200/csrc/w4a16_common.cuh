@@ -36,6 +36,8 @@ struct W4Params {
     int group_kb;      // k-blocks per scale group (group_size / 64)
     int group_shift;   // log2(group_kb) when it is a power of two, else -1
     int* status;
+    int* block_done;   // optional: block_done[tt] is incremented when a column tile of token block tt has been written
+    int tt_major;      // 1: units walk all column tiles of a token block before the next block (set with block_done)
 };
 
 __device__ __forceinline__ void w4_report(int* status, int role, int detail) {
@@ -74,8 +76,15 @@ __device__ __forceinline__ bool w4_unit(const W4Params& p, int ui, W4Unit& u) {
         u.sl = unit % p.split;
         u.nsl = p.split;
         const int t = unit / p.split;
-        u.tt = t % p.t_tiles;
-        u.nt = t / p.t_tiles;
+        if (p.tt_major) {
+            // token block by token block: a block's output is complete after its n_tiles tiles, early in
+            // the launch, so that a consumer (the sum over the ranks) can follow the kernel block by block
+            u.nt = t % p.n_tiles;
+            u.tt = t / p.n_tiles;
+        } else {
+            u.tt = t % p.t_tiles;
+            u.nt = t / p.t_tiles;
+        }
         u.kb0 = static_cast<int>(static_cast<long long>(u.sl) * p.kb_total / p.split);
         u.kb1 = static_cast<int>(static_cast<long long>(u.sl + 1) * p.kb_total / p.split);
         return true;

@@ -27,6 +27,10 @@
 #include "ptx.cuh"
 #include "w4a16_common.cuh"
 
+#ifndef W4_PREFILL_REGS
+#define W4_PREFILL_REGS 104
+#endif
+
 namespace wb {
 
 template <int BT, bool WM>
@@ -53,6 +57,10 @@ struct W4Cfg {
     static_assert(TMEM_NEED <= 512, "TMEM budget");
     static constexpr int STAGE_OUT_BYTES = 32 * 64 * 4;  // silu(gate)*up hand-over between epilogue warps
     static constexpr int SMEM_BYTES = S * S_STAGE + R * W4_SLOT_BYTES + 1024 + 512 + STAGE_OUT_BYTES;
+    // Registers per thread. The prefill tile is held to 104 (measured: as fast as 128; 96 costs 5 %), which
+    // leaves 12 K of the SM's registers, and its shared memory leaves 8 KB: enough for a 192-thread CTA of the
+    // all-reduce kernel to run on the same SM while this persistent kernel occupies every SM.
+    static constexpr int MAX_REGS = (BT >= 256 && !WM) ? W4_PREFILL_REGS : 128;
 };
 
 
@@ -65,7 +73,7 @@ __device__ __forceinline__ void dq_word_store(uint32_t dst, uint32_t w, __half2 
 }
 
 template <int BT, bool WM>
-__global__ void __launch_bounds__(W4_THREADS, 1)
+__global__ void __maxnreg__((W4Cfg<BT, WM>::MAX_REGS))
 w4a16_gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ CUtensorMap tmap_w,
                   const __grid_constant__ CUtensorMap tmap_sc, const W4Params p) {
     using Cfg = W4Cfg<BT, WM>;
@@ -399,6 +407,16 @@ w4a16_gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_const
             acc ^= 1;
             if (acc == 0) acc_ph ^= 1u;
 
+            if (p.block_done != nullptr && nsl == 1) {
+                // tell whoever follows this kernel that one more column tile of token block tt is in
+                // memory: the barrier orders the 128 threads' stores before thread 0's system-scope
+                // fence (the readers may sit behind NVLink), which is cumulative over them
+                named_barrier_sync(1, 128);
+                if (et == 0) {
+                    __threadfence_system();
+                    atomicAdd(p.block_done + tt, 1);
+                }
+            }
             if (nsl > 1) {
                 // the last slice of this tile to finish sums all partials in slice order
                 // One release for the whole CTA: the barrier orders the 128 threads' partial stores
@@ -659,10 +677,27 @@ extern "C" int wmma_ops_w4a16_gemm(const void* A, const void* qweight, const voi
                                   workspace, workspace_bytes, status, stream_);
 }
 
+extern "C" int wmma_ops_w4a16_token_block(int M) { return wb::w4_pick_bt(M < 1 ? 1 : M); }
+
+extern "C" int wmma_ops_w4a16_gemm_blocks(const void* A, const void* qweight, const void* scales, void* C, int M,
+                                          int N, int K, int group_size, int split_k, int out_mode, float alpha,
+                                          float in_scale, void* workspace, size_t workspace_bytes, int* block_done,
+                                          int* status, void* stream_);
+
 extern "C" int wmma_ops_w4a16_gemm_ex(const void* A, const void* qweight, const void* scales, void* C, int M,
                                       int N, int K, int group_size, int split_k, int out_mode, float alpha, float in_scale,
                                       void* workspace, size_t workspace_bytes, int* status, void* stream_) {
+    return wmma_ops_w4a16_gemm_blocks(A, qweight, scales, C, M, N, K, group_size, split_k, out_mode, alpha, in_scale,
+                                      workspace, workspace_bytes, nullptr, status, stream_);
+}
+
+extern "C" int wmma_ops_w4a16_gemm_blocks(const void* A, const void* qweight, const void* scales, void* C, int M,
+                                          int N, int K, int group_size, int split_k, int out_mode, float alpha,
+                                          float in_scale, void* workspace, size_t workspace_bytes, int* block_done,
+                                          int* status, void* stream_) {
     using namespace wb;
+    WB_REQUIRE(block_done == nullptr || (M > W4_STREAM_MAX_M && split_k <= 1), WMMA_OPS_ERR_INVALID,
+               "w4a16: block completion counters are for products with more than %d rows and no K split", W4_STREAM_MAX_M);
     WB_REQUIRE(out_mode >= WMMA_OPS_W4_OUT_F32 && out_mode <= WMMA_OPS_W4_OUT_F16_SILU_MUL, WMMA_OPS_ERR_INVALID,
                "w4a16: unknown out_mode %d", out_mode);
     WB_REQUIRE(out_mode != WMMA_OPS_W4_OUT_F16_SILU_MUL || N % 128 == 0, WMMA_OPS_ERR_INVALID,
@@ -707,6 +742,8 @@ extern "C" int wmma_ops_w4a16_gemm_ex(const void* A, const void* qweight, const 
     for (int sh = 0; sh < 24; ++sh)
         if ((1 << sh) == p.group_kb) p.group_shift = sh;
     p.status = status;
+    p.block_done = block_done;
+    p.tt_major = block_done != nullptr ? 1 : 0;
     p.split = plan.split;
     p.balanced = plan.balanced;
     p.max_slices = plan.max_slices;

@@ -6,6 +6,7 @@ from __future__ import annotations
 
 import ctypes
 import os
+import weakref
 from typing import Optional, Tuple
 
 import torch
@@ -47,6 +48,14 @@ def check_status(device=None) -> None:
         )
 
 
+_reset_hooks: "weakref.WeakSet" = weakref.WeakSet()
+
+
+def _register_reset(obj) -> None:
+    """obj.reset() is called (while obj lives) whenever reset_workspaces runs for obj.device."""
+    _reset_hooks.add(obj)
+
+
 def reset_workspaces(device) -> None:
     """Zero-fills every zero-initialised scratch buffer this module holds for `device` (W4A16
     partial sums and their arrival counters). Called after a non-zero status word."""
@@ -55,6 +64,9 @@ def reset_workspaces(device) -> None:
         if zero_init and dtype == device.type and index == device.index:
             for b in bufs:
                 b.zero_()
+    for obj in list(_reset_hooks):
+        if torch.device(obj.device) == device:
+            obj.reset()
 
 
 def _workspace(device: torch.device, nbytes: int, zero_init: bool = False) -> torch.Tensor:

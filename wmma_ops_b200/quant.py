@@ -100,9 +100,15 @@ def interleave_gate_up(codes: torch.Tensor, scales: torch.Tensor) -> Tuple[torch
     return codes[:, order].contiguous(), scales[:, order].contiguous()
 
 
+def w4a16_token_block(M: int) -> int:
+    """Rows per token block of the tcgen05 W4A16 kernel for a product with M rows (see block_done)."""
+    return int(_lib.load().wmma_ops_w4a16_token_block(int(M)))
+
+
 def matmul_w4a16(A: torch.Tensor, qweight: torch.Tensor, scales: torch.Tensor, group_size: int = 128,
                  split_k: int = 0, out_dtype: torch.dtype = torch.float32, alpha: float = 1.0,
-                 epilogue: str = "none", out: Optional[torch.Tensor] = None, in_scale: float = 1.0) -> torch.Tensor:
+                 epilogue: str = "none", out: Optional[torch.Tensor] = None, in_scale: float = 1.0,
+                 block_done: Optional[torch.Tensor] = None) -> torch.Tensor:
     """C [M,N] = A fp16 [M,K] @ dequant(qweight, scales); the weights are expanded inside the kernel,
     never written to memory. split_k=0 lets the library choose: up to 16 rows go to the decode
     kernel (every CTA owns a range of columns and streams their packed weights over all of K; exact
@@ -113,7 +119,12 @@ def matmul_w4a16(A: torch.Tensor, qweight: torch.Tensor, scales: torch.Tensor, g
     half(alpha * acc). epilogue="silu_mul" (weights prepared with interleave_gate_up) returns
     half(alpha * silu(in_scale * gate) * (in_scale * up)) of shape [M, N/2]; in_scale stands for a scale
     of A that the caller left out (A @ W is linear in A). `out`, if given, is the contiguous tensor of that
-    shape and dtype the result is written to (for example a buffer in symmetric memory)."""
+    shape and dtype the result is written to (for example a buffer in symmetric memory).
+
+    block_done (M > 16, no K split): int32 CUDA tensor, zero before the call, one entry per block of
+    w4a16_token_block(M) rows. The kernel then works through the rows block by block and adds one to
+    block_done[b] whenever a 128-column tile of block b is in memory, so that a kernel running beside it
+    can consume finished blocks (a block is complete at ceil(N / 128))."""
     _require(A.is_cuda and qweight.is_cuda and scales.is_cuda, "Inputs must be CUDA tensors")
     _require(A.device == qweight.device and A.device == scales.device, "Inputs must be on same device")
     _require(A.dtype == torch.float16, "Inputs must be float16")
@@ -146,15 +157,22 @@ def matmul_w4a16(A: torch.Tensor, qweight: torch.Tensor, scales: torch.Tensor, g
         C = out
     if M == 0:
         return C
+    done_ptr = None
+    if block_done is not None:
+        _require(M > 16 and split_k in (0, 1), "block_done needs more than 16 rows and no K split")
+        _require(block_done.is_cuda and block_done.device == dev and block_done.dtype == torch.int32
+                 and block_done.is_contiguous() and block_done.numel() * w4a16_token_block(M) >= M,
+                 "block_done must be a contiguous int32 CUDA tensor with one entry per token block")
+        done_ptr = block_done.data_ptr()
     with _device_guard(dev):
         ws_ptr, ws_bytes = None, 0
         need = lib.wmma_ops_w4a16_workspace_bytes(M, N, K, split_k)   # split_k = 0: the library's own plan
         if need > 0:
             ws = _workspace(dev, need, zero_init=True)
             ws_ptr, ws_bytes = ws.data_ptr(), ws.numel()
-        rc = lib.wmma_ops_w4a16_gemm_ex(A.data_ptr(), qweight.data_ptr(), scales.data_ptr(), C.data_ptr(), M, N, K,
-                                        group_size, split_k, mode, float(alpha), float(in_scale), ws_ptr, ws_bytes,
-                                        _status_word(dev).data_ptr(), _stream(dev))
+        rc = lib.wmma_ops_w4a16_gemm_blocks(A.data_ptr(), qweight.data_ptr(), scales.data_ptr(), C.data_ptr(), M, N, K,
+                                            group_size, split_k, mode, float(alpha), float(in_scale), ws_ptr, ws_bytes,
+                                            done_ptr, _status_word(dev).data_ptr(), _stream(dev))
         _lib.check(rc)
         _post(dev)
     return C

@@ -95,8 +95,12 @@ class ShardedDecoderLinears:
                  group: int = GROUP, matmul: Optional[Callable] = None, all_reduce: Optional[Callable] = None,
                  reduce_dtype: torch.dtype = torch.float32, chunks: int = 1, switch=None,
                  attention: Optional[Tuple[int, bool]] = None, head_dim: int = 128,
-                 attention_fn: Optional[Callable] = None):
+                 attention_fn: Optional[Callable] = None, follow: bool = False):
         self.world = world
+        # with a switch: the sum of a row-parallel output runs beside the GEMM that produces it, token block
+        # by token block, on a helper stream (SwitchAllReduce.reduce_following)
+        self.follow = bool(follow) and switch is not None and world > 1
+        self._helpers: Dict[int, torch.cuda.Stream] = {}
         # (seq_len, causal): run the attention core between QKV and O on this rank's heads (the Q, K
         # and V sections are cut by rank, so a rank holds whole heads and attention needs no exchange);
         # None keeps the linears-only workload, where O's input is the rank's slice of the Q section
@@ -135,6 +139,29 @@ class ShardedDecoderLinears:
             return None
         import torch.distributed as dist
         return dist.all_reduce(t, op=dist.ReduceOp.SUM, async_op=async_op)
+
+    def _switch_row_parallel(self, a: torch.Tensor, name: str, slot: int, row0: int = 0,
+                             channel: Optional[int] = None) -> torch.Tensor:
+        """a @ W_local written into rows [row0, row0 + len(a)) of the switch's buffer `slot` and summed over the
+        ranks; returns the fp16 sums. With follow, the sum kernel is launched on a helper stream right after the
+        GEMM and consumes finished token blocks while the GEMM computes the next ones."""
+        from .quant import w4a16_token_block
+        sw, rows = self.switch, a.shape[0]
+        out = sw.buffer(slot)[row0:row0 + rows]
+        if not (self.follow and rows > 128 and row0 % 32 == 0):
+            self._w4(a, name, out_dtype=self.reduce_dtype, out=out)
+            return sw.reduce(slot, rows, row0=row0, channel=channel)
+        cur = torch.cuda.current_stream(a.device)
+        helper = self._helpers.get(cur.cuda_stream)
+        if helper is None:
+            helper = self._helpers[cur.cuda_stream] = torch.cuda.Stream(device=a.device)
+        helper.wait_stream(cur)      # the sum may not overtake earlier readers of the buffer
+        self._w4(a, name, out_dtype=self.reduce_dtype, out=out, block_done=sw.counters(slot, row0))
+        tiles = (out.shape[1] + 127) // 128
+        with torch.cuda.stream(helper):
+            part = sw.reduce_following(slot, rows, w4a16_token_block(rows), tiles, row0=row0, channel=channel)
+        cur.wait_stream(helper)
+        return part
 
     def _row_parallel(self, x: torch.Tensor, name: str) -> torch.Tensor:
         """x @ W_local (K-sharded) summed over ranks. Token chunks let the all-reduce of one
@@ -207,12 +234,9 @@ class ShardedDecoderLinears:
             # partial outputs (fp16, or the fp32 accumulators) go straight into symmetric memory and are
             # summed through the switch by one launch; the sums are fp16, so the 1/4 scaling of the MLP
             # input is exact and is folded into the gate/up GEMM instead of a pass over the tensor
-            T = x.shape[0]
-            self._w4(o_in, "o", out_dtype=out_dt, out=self.switch.buffer(0, T))
-            attn_out = self.switch.reduce(0, T)
+            attn_out = self._switch_row_parallel(o_in, "o", 0)
             act = self._w4(attn_out, "gate_up", epilogue="silu_mul", alpha=GLUE_SCALE, in_scale=GLUE_SCALE)
-            self._w4(act, "down", out_dtype=out_dt, out=self.switch.buffer(1, T))
-            mlp_out = self.switch.reduce(1, T)
+            mlp_out = self._switch_row_parallel(act, "down", 1)
             return attn_out, mlp_out
         self._matmul = lambda a, name: self._w4(a, name, out_dtype=out_dt)  # noqa: E731
         attn_out = self._row_parallel(o_in, "o")
@@ -250,8 +274,7 @@ class ShardedDecoderLinears:
                     # partial output into the symmetric buffer, summed through the switch by the
                     # library's kernel on this side stream (a few CTAs; the other stream's GEMM
                     # keeps the remaining SMs busy)
-                    self._w4(o_in, "o", out_dtype=out_dt, out=self.switch.buffer(0)[a:b])
-                    part = self.switch.reduce(0, b - a, row0=a, channel=c % 2)
+                    part = self._switch_row_parallel(o_in, "o", 0, row0=a, channel=c % 2)
                     work = None
                 else:
                     part = self._w4(o_in, "o", out_dtype=out_dt)
@@ -271,8 +294,7 @@ class ShardedDecoderLinears:
                     h = (part * GLUE_SCALE).to(torch.float16)
                     act = self._w4(h, "gate_up", epilogue="silu_mul", alpha=GLUE_SCALE)
                 if self.switch is not None:
-                    self._w4(act, "down", out_dtype=out_dt, out=self.switch.buffer(1)[a:b])
-                    part2 = self.switch.reduce(1, b - a, row0=a, channel=2 + c % 2)
+                    part2 = self._switch_row_parallel(act, "down", 1, row0=a, channel=2 + c % 2)
                     work2 = None
                 else:
                     part2 = self._w4(act, "down", out_dtype=out_dt)
