@@ -372,12 +372,21 @@ def measure_layer(w, dev, rank, world, steps):
             ms = time_region(run, max(3, min(steps, 10)), world, dev)
             attn, mlp = outputs()
             torch.cuda.synchronize()
-            w.check_status(dev)      # a bounded wait that gave up is an error of the variant, not a timing
+            # a bounded wait that gave up on any rank is an error of the variant, not a timing; the ranks agree
+            # on that through the same all-reduce as the errors, so that none of them leaves the others in it
+            gave_up = 0.0
+            try:
+                w.check_status(dev)
+            except RuntimeError as err:
+                gave_up, why = 1.0, str(err)
             errs = torch.tensor([og.rel_frobenius(attn[:sample].float().cpu(), refs[0].cpu()),
-                                 og.rel_frobenius(mlp[:sample].float().cpu(), refs[1].cpu())], dtype=torch.float64, device=dev)
+                                 og.rel_frobenius(mlp[:sample].float().cpu(), refs[1].cpu()), gave_up],
+                                dtype=torch.float64, device=dev)
             if world > 1:
                 dist.all_reduce(errs, op=dist.ReduceOp.MAX)
             e = errs.tolist()
+            if e[2] > 0:
+                raise RuntimeError(why if gave_up else "a bounded wait gave up on another rank")
             row = {"ms": ms, "tflops": flops / ms / 1e9, "tokens_per_s": tokens / ms * 1e3, "attn_err": e[0], "mlp_err": e[1],
                    "within_tol": bool(e[0] <= LAYER_TOL and e[1] <= LAYER_TOL)}
             if note:

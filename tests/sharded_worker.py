@@ -55,14 +55,20 @@ def main():
         def check(label, layer, tol_attn, tol_mlp):
             attn, mlp = layer(xd)
             torch.cuda.synchronize()
-            w.check_status(dev)
-            errs = torch.tensor([og.rel_frobenius(attn.float().cpu(), ref_attn), og.rel_frobenius(mlp.float().cpu(), ref_mlp)],
-                                dtype=torch.float64, device=dev)
+            gave_up = 0.0
+            try:
+                w.check_status(dev)
+            except RuntimeError as err:     # reported through the all-reduce below: no rank leaves the others in it
+                gave_up = 1.0
+                print(f"rank {rank} {label}: {err}", flush=True)
+            errs = torch.tensor([og.rel_frobenius(attn.float().cpu(), ref_attn), og.rel_frobenius(mlp.float().cpu(), ref_mlp),
+                                 gave_up], dtype=torch.float64, device=dev)
             dist.all_reduce(errs, op=dist.ReduceOp.MAX)       # every rank holds its own copy: the worst one counts
-            e1, e2 = errs.tolist()
+            e1, e2, bad = errs.tolist()
             if rank == 0:
-                print(f"world={world} {label}: attn_err={e1:.2e} mlp_err={e2:.2e} (max over ranks)", flush=True)
-            return e1 < tol_attn and e2 < tol_mlp
+                print(f"world={world} {label}: attn_err={e1:.2e} mlp_err={e2:.2e} (max over ranks)"
+                      + (" A BOUNDED WAIT GAVE UP" if bad else ""), flush=True)
+            return e1 < tol_attn and e2 < tol_mlp and not bad
 
         w.set_sm_margin(16)
         for rdt, chunks, tol in ((torch.float32, 1, GATE), (torch.float16, 1, FP16_PARTIALS), (torch.float16, 2, FP16_PARTIALS)):
