@@ -238,7 +238,7 @@ int wmma_ops_switch_allreduce(const void* mc_in, void* mc_out, size_t n_values, 
  *   mc_in / mc_out  multicast addresses of the first of the `rows` rows (cols % 8 == 0), as above.
  *   block_done      the counters given to the GEMM; seen: as many zero-initialised ints of device memory.
  *                   Both are zero again when the call has completed.
- *   max_ctas        <= 0: 32. Up to four CTAs share a token block when there are fewer blocks than CTAs.
+ *   max_ctas        <= 0: 32. Up to eight CTAs share a token block when there are fewer blocks than CTAs.
  * Launch the GEMM first and leave it room to become resident: either as many SMs free as this call has
  * CTAs (wmma_ops_set_sm_margin), or a product with more than 128 rows, whose kernel leaves room for one
  * CTA of this one on every SM. A CTA whose GEMM does not finish a block within about a second records

@@ -386,9 +386,9 @@ extern "C" int wmma_ops_switch_allreduce_following(const void* mc_in, void* mc_o
     const size_t row_vecs = static_cast<size_t>(cols) / 8;
     int ctas = max_ctas > 0 ? max_ctas : 32;
     if (ctas > SW_MAX_CTAS) ctas = SW_MAX_CTAS;
-    // whole groups of `parts` CTAs per token block: up to 4 CTAs share a block when there are few blocks
+    // whole groups of `parts` CTAs per token block: up to 8 CTAs share a block when there are few blocks
     int parts = ctas / n_blocks;
-    parts = parts < 1 ? 1 : parts > 4 ? 4 : parts;
+    parts = parts < 1 ? 1 : parts > 8 ? 8 : parts;
     int groups = ctas / parts;
     if (groups > n_blocks) groups = n_blocks;
     ctas = groups * parts;
