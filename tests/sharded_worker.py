@@ -111,6 +111,27 @@ def main():
                 layer = None
                 sw.max_ctas = 0
                 w.set_sm_margin(0)
+            # Failure path, made without any fault: a following sum whose GEMM is never launched. Every CTA's
+            # wait for its token block runs out (about a second), the kernel records {6, rank, CTA, block},
+            # still meets the other ranks and returns; check_status raises and clears the counters, and the
+            # next ordinary sum works.
+            sw16.max_ctas = 8
+            sw16.reduce_following(0, 512, 256, 32)
+            torch.cuda.synchronize()
+            try:
+                w.check_status(dev)
+                seen = ""
+            except RuntimeError as err:
+                seen = str(err)
+            gave_up = "code=6" in seen and f"role={rank}" in seen
+            if not gave_up:
+                print(f"rank {rank}: expected the following sum to give up with code 6, saw '{seen}'", flush=True)
+            ok = gave_up and ok
+            ok = bool(sw16._blocks.abs().sum().item() == 0) and ok      # counters cleared by the reset hook
+            sw16.max_ctas = 0
+            layer = sharded.ShardedDecoderLinears(local, world=world, reduce_dtype=torch.float16, switch=sw16)
+            ok = check("switch fp16 partials after a sum that gave up", layer, FP16_PARTIALS, FP16_PARTIALS) and ok
+            layer = None
     except Exception:
         ok = False
         print(f"rank {rank} failed:\n{traceback.format_exc()}", flush=True)
