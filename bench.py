@@ -472,6 +472,22 @@ def measure_layer(w, dev, rank, world, steps):
             del run, outs, layer
         except Exception as e:
             out["nccl_fp16_reduce_cuda_graph"] = {"error": f"{type(e).__name__}: {str(e)[:200]}"}
+    # ---- what the exchange costs: the same rank-local work with the two sums left out (the outputs are then
+    # partial sums, so nothing is checked): layer.ms minus this is the exposed part of the exchange, this
+    # minus T(1)/N is what the smaller per-rank GEMMs lose
+    compute_only = None
+    if world > 1:
+        try:
+            layer = sharded.ShardedDecoderLinears(local, world=world, reduce_dtype=torch.float16,
+                                                  all_reduce=lambda t, async_op=False: None)
+            run, outs = graphed(layer)
+            for _ in range(3):
+                run()
+            compute_only = {"ms": time_region(run, max(3, min(steps, 10)), world, dev),
+                            "note": "one rank's GEMMs and glue, sums left out, CUDA-graph replay; not a result"}
+            del run, outs, layer
+        except Exception as e:
+            compute_only = {"error": f"{type(e).__name__}: {str(e)[:200]}"}
     # ---- the whole block: the attention core (4 sequences of 2048 tokens, causal, heads cut by rank)
     # between the QKV and the O projection. Checked the same way: causal attention over the first 256
     # tokens of the first sequence does not depend on what follows them.
@@ -525,6 +541,8 @@ def measure_layer(w, dev, rank, world, steps):
         res["with_attention"] = {"workload": "the same layer with causal attention (4 x 2048 tokens, 32 heads of 128) between QKV and O",
                                  "ms": best_a["ms"], "tflops": best_a["tflops"], "attn_err": best_a["attn_err"],
                                  "mlp_err": best_a["mlp_err"], "tolerance": 2e-3, "variants": with_attention}
+    if compute_only is not None:
+        res["compute_only"] = compute_only
     if world > 1:
         # bytes each GPU must send (and receive) for the two sums of one layer: every rank's partial
         # [tokens, 4096] leaves once and the summed result comes back once, minus the local 1/world

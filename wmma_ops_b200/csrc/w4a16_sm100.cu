@@ -760,6 +760,8 @@ extern "C" int wmma_ops_w4a16_gemm_blocks(const void* A, const void* qweight, co
         p.max_slices = 1;
         return w4_decode_launch(p, dp, stream);
     }
+    WB_REQUIRE(block_done == nullptr || !plan.partials(), WMMA_OPS_ERR_INVALID,
+               "w4a16: block completion counters need a plan without partial sums (pass split_k = 1)");
     WB_REQUIRE(out_mode == WMMA_OPS_W4_OUT_F32 || !plan.partials(), WMMA_OPS_ERR_INVALID,
                "w4a16: fp16 / fused outputs need a plan without partial sums (pass split_k = 1)");
     if (plan.partials()) {
