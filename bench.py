@@ -720,24 +720,25 @@ def run_kernel_only(args, w, dev, A, B):
             q, sc = sets[state["i"] % len(sets)]
             state["i"] += 1
             return w.matmul_w4a16(X, q, sc, 128)
-    elif name.startswith("w4a16_f16_"):
-        # w4a16_f16_<M>x<K>x<N>[_blocks]: one fp16-output product of the sharded layer's shapes; with "_blocks"
+    elif name.startswith("w4a16_f16_") or name.startswith("w4a16_f32_"):
+        # w4a16_f16_<M>x<K>x<N>[_blocks] (or w4a16_f32_...): one product of the sharded layer's shapes; with "_blocks"
         # the kernel walks token block by token block and counts finished tiles (the producer side of the
         # all-reduce that follows its GEMM)
+        odt = torch.float16 if name.startswith("w4a16_f16_") else torch.float32
         dims = name[len("w4a16_f16_"):].replace("_blocks", "")
         M, K, N = (int(v) for v in dims.split("x"))
         codes = torch.randint(0, 16, (K, N), generator=gen, device=dev, dtype=torch.uint8)
         scales = (torch.rand(K // 64, N, generator=gen, device=dev) * 0.019 + 0.001).half()
         q, sc = w.int4_prepack(codes, scales, 64)
         X = torch.randn(M, K, generator=gen, device=dev).half()
-        out = torch.empty(M, N, dtype=torch.float16, device=dev)
+        out = torch.empty(M, N, dtype=odt, device=dev)
         bt = w.w4a16_token_block(M)
         done = torch.zeros((M + bt - 1) // bt, dtype=torch.int32, device=dev) if name.endswith("_blocks") else None
 
         def fn():
             if done is not None:
                 done.zero_()
-            return w.matmul_w4a16(X, q, sc, 64, out_dtype=torch.float16, out=out, block_done=done)
+            return w.matmul_w4a16(X, q, sc, 64, out_dtype=odt, out=out, block_done=done)
     elif name in ("fmha_s2048", "fmha_s2048_causal"):
         Q = torch.randn(4, 32, 2048, 128, generator=gen, device=dev).half()
         Kt = torch.randn(4, 32, 2048, 128, generator=gen, device=dev).half()
