@@ -409,11 +409,70 @@ w4a16_gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_const
                                 p.C16[static_cast<size_t>(t) * p.N + n] = __float2half_rn(p.alpha * __uint_as_float(v[j]));
                         }
                     }
+                } else if (vec16) {
+                    // Fused gate/up: the tile's rows 0..63 are gate columns and rows 64..127 the up columns of
+                    // the same 64 outputs, so thread f of the gate warps and thread f of the up warps hold the
+                    // two factors of output f for the chunk's CH tokens. They split the tokens: each sends the
+                    // other its values for the half it does not compute (through shared memory), so all four
+                    // warps do half of the exponentials each; the products go, as fp16, into a [token][output]
+                    // tile in shared memory and leave as 16-byte vectors (eight lanes per 128-byte row).
+                    constexpr int H = CH / 2;
+                    const bool is_gate = row < 64;
+                    const int fl = row & 63;
+                    // gate -> up: gate values of tokens [H, CH); up -> gate: up values of tokens [0, H)
+                    const uint32_t send = out_stage + (is_gate ? 0 : H * 64 * 4) + fl * 4;
+                    const uint32_t recv = out_stage + (is_gate ? H * 64 * 4 : 0) + fl * 4;
+#pragma unroll
+                    for (int jj = 0; jj < H; ++jj)
+                        asm volatile("st.shared.u32 [%0], %1;" ::"r"(send + jj * 64 * 4), "r"(is_gate ? v[H + jj] : v[jj])
+                                     : "memory");
+                    named_barrier_sync(3, 128);
+                    float act[H];
+#pragma unroll
+                    for (int jj = 0; jj < H; ++jj) {
+                        uint32_t other;
+                        asm volatile("ld.shared.u32 %0, [%1];" : "=r"(other) : "r"(recv + jj * 64 * 4) : "memory");
+                        const float gv = __uint_as_float(is_gate ? v[jj] : other);
+                        const float uv = __uint_as_float(is_gate ? other : v[H + jj]);
+                        const float gte = p.in_scale * gv;
+                        act[jj] = p.alpha * __fdividef(gte, 1.f + __expf(-gte)) * (p.in_scale * uv);
+                    }
+                    named_barrier_sync(3, 128);  // every value sent has been read: the buffer becomes the output tile
+                    const int tb = is_gate ? 0 : H;  // first token (inside the chunk) this thread computed
+#pragma unroll
+                    for (int jj = 0; jj < H; jj += 2) {
+                        const __half2 h2 = __floats2half2_rn(act[jj], act[jj + 1]);
+                        const uint32_t hb = *reinterpret_cast<const uint32_t*>(&h2);
+                        asm volatile("st.shared.u16 [%0], %1;" ::"r"(out_stage + ((tb + jj) * 64 + fl) * 2),
+                                     "h"(static_cast<unsigned short>(hb & 0xffffu))
+                                     : "memory");
+                        asm volatile("st.shared.u16 [%0], %1;" ::"r"(out_stage + ((tb + jj + 1) * 64 + fl) * 2),
+                                     "h"(static_cast<unsigned short>(hb >> 16))
+                                     : "memory");
+                    }
+                    named_barrier_sync(3, 128);
+                    const int ldo = p.N / 2;
+#pragma unroll
+                    for (int ps = 0; ps < (CH * 8 + 127) / 128; ++ps) {
+                        const int idx = ps * 128 + et;  // 16-byte vector of the CH x 64 tile
+                        const int r = idx >> 3;
+                        const int cv = (idx & 7) * 8;
+                        if (r < CH) {
+                            uint4 val;
+                            asm volatile("ld.shared.v4.u32 {%0, %1, %2, %3}, [%4];"
+                                         : "=r"(val.x), "=r"(val.y), "=r"(val.z), "=r"(val.w)
+                                         : "r"(out_stage + (r * 64 + cv) * 2)
+                                         : "memory");
+                            const int t = t0 + c * CH + r;
+                            const int ff = nt * 64 + cv;  // the output has N / 2 columns, a multiple of 64
+                            if (t < p.M && ff < ldo && WB_DEBUG_INDEX(t >= 0 && ff >= 0 && ff + 8 <= ldo, p.status, 103, ff))
+                                *reinterpret_cast<uint4*>(p.C16 + static_cast<size_t>(t) * ldo + ff) = val;
+                        }
+                    }
+                    named_barrier_sync(3, 128);  // the tile is rewritten by the next chunk
                 } else {
-                    // Fused gate/up: the tile's rows 0..63 are gate columns and rows 64..127 the up
-                    // columns of the same 64 outputs. The up warps pass their values through shared
-                    // memory ([token][row] so that lanes hit consecutive banks); the gate warps
-                    // compute alpha * silu(gate) * up and store fp16.
+                    // fused gate/up with an output that is not 16-byte aligned: the up warps pass their values
+                    // through shared memory, the gate warps compute and store element by element
                     if (row >= 64) {
 #pragma unroll
                         for (int j = 0; j < CH; ++j)
