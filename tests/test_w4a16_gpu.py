@@ -360,3 +360,32 @@ def test_block_completion_counters(M, N, K):
     assert done.tolist() == [(N + 127) // 128] * blocks
     with pytest.raises(RuntimeError):
         w.matmul_w4a16(x[:8], q, scales, 128, block_done=done)
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("epilogue", ["none", "silu_mul"])
+def test_fp16_outputs_at_an_unaligned_address(epilogue):
+    """The fp16 epilogues store 16-byte vectors when the output is 16-byte aligned and fall back to
+    element-wise stores when it is not: both must give the same bits."""
+    torch.manual_seed(3)
+    dev = torch.device("cuda", 0)
+    M, K, N = 300, 256, 384
+    codes = torch.randint(0, 16, (K, N), dtype=torch.uint8, device=dev)
+    scales = (torch.rand((K // 128, N), device=dev) * 0.02 + 0.005).half()
+    if epilogue == "silu_mul":
+        codes, scales = w.interleave_gate_up(codes, scales)
+    q, sc = w.int4_prepack(codes, scales, 128)
+    x = (torch.randn((M, K), device=dev) * 0.5).half()
+    kw = dict(out_dtype=torch.float16, alpha=0.5) if epilogue == "none" else dict(epilogue="silu_mul", alpha=0.5, in_scale=0.5)
+    aligned = w.matmul_w4a16(x, q, sc, 128, **kw)
+    cols = aligned.shape[1]
+    flat = torch.zeros(M * cols + 8, dtype=torch.float16, device=dev)
+    out = flat[1:1 + M * cols].view(M, cols)          # 2 bytes past a 16-byte boundary
+    assert out.data_ptr() % 16 == 2 and out.is_contiguous()
+    w.matmul_w4a16(x, q, sc, 128, out=out, **kw)
+    w.check_status()
+    if epilogue == "none":
+        assert torch.equal(out, aligned)
+    else:       # the fallback divides with IEEE rounding, the vector path with the fast reciprocal
+        assert torch.allclose(out.float(), aligned.float(), rtol=2e-3, atol=1e-4)
+    assert flat[0] == 0 and torch.all(flat[1 + M * cols:] == 0)
