@@ -148,6 +148,16 @@ __device__ __forceinline__ uint32_t dq_pair(uint32_t t, __half2 scale2) {
     return *reinterpret_cast<const uint32_t*>(&r);
 }
 
+// The same for two codes that sit in bits 4..7 and 20..23 of t (masked with 0x00F000F0, not shifted):
+// 0x5400 | (code << 4) is the fp16 number 64 + code (the mantissa step at 64 is 1/16), so subtracting 72
+// gives code - 8 exactly. Saves the shift that would bring the nibble down to bit 0.
+__device__ __forceinline__ uint32_t dq_pair_hi(uint32_t t, __half2 scale2) {
+    const uint32_t h = t | 0x54005400u;
+    const __half2 v = __hsub2(*reinterpret_cast<const __half2*>(&h), __half2half2(__ushort_as_half(0x5480)));
+    const __half2 r = __hmul2(v, scale2);
+    return *reinterpret_cast<const uint32_t*>(&r);
+}
+
 // ---------------------------------------------------------------- decode kernel
 // (w4a16_decode_sm100.cu) for products with at most W4_STREAM_MAX_M activation rows.
 constexpr int W4_STREAM_MAX_M = 16;

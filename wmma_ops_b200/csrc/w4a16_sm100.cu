@@ -65,10 +65,11 @@ struct W4Cfg {
 
 
 __device__ __forceinline__ void dq_word_store(uint32_t dst, uint32_t w, __half2 scale2) {
+    const uint32_t w8 = w >> 8;
     const uint32_t a = dq_pair(w & 0x000F000Fu, scale2);
-    const uint32_t b = dq_pair((w >> 4) & 0x000F000Fu, scale2);
-    const uint32_t c = dq_pair((w >> 8) & 0x000F000Fu, scale2);
-    const uint32_t d = dq_pair((w >> 12) & 0x000F000Fu, scale2);
+    const uint32_t b = dq_pair_hi(w & 0x00F000F0u, scale2);
+    const uint32_t c = dq_pair(w8 & 0x000F000Fu, scale2);
+    const uint32_t d = dq_pair_hi(w8 & 0x00F000F0u, scale2);
     asm volatile("st.shared.v4.u32 [%0], {%1, %2, %3, %4};" ::"r"(dst), "r"(a), "r"(b), "r"(c), "r"(d));
 }
 
