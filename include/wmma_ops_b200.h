@@ -255,6 +255,13 @@ int wmma_ops_switch_allreduce_following(const void* mc_in, void* mc_out, int row
 int wmma_ops_fmha_fwd(const void* Q, const void* K, const void* V, void* O, int B, int H, int S,
                       int D, float scale, int causal, int* status, void* stream);
 
+/* The same for tensors that are not contiguous [B,H,S,D]: D is contiguous, and `strides` holds, in elements,
+ * the distances between consecutive tokens, heads and sequences of Q, then K, V and O (12 values; multiples
+ * of 8, token rows at least D apart). E.g. the Q section of a packed projection output [tokens, 3, H, D]
+ * has strides {3 H D, D, S 3 H D}. Nothing is copied: the kernel's tensor maps are (D, token, head, sequence). */
+int wmma_ops_fmha_fwd_strided(const void* Q, const void* K, const void* V, void* O, int B, int H, int S, int D,
+                              const long long* strides, float scale, int causal, int* status, void* stream);
+
 /* The same attention for decode shapes: Sq <= 16 query rows per (b,h) against Skv >= Sq keys and
  * values (Q, O [B,H,Sq,D]; K, V [B,H,Skv,D]; fp16, contiguous). With causal != 0 query row i sees
  * the keys 0 .. Skv - Sq + i. The key range is cut into splits over the SMs; with more than one

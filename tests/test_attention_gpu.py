@@ -178,3 +178,25 @@ def test_errors(cuda):
     with pytest.raises(RuntimeError, match="may be longer than Q"):
         w.flash_attention(torch.cat([Q, Q], dim=2)[:, :, :8].contiguous(), Q[:, :, :4].contiguous(), Q[:, :, :4].contiguous())
     assert w.flash_attention(Q[:, :0], Q[:, :0], Q[:, :0]).shape == (1, 0, 64, 128)
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("causal", [False, True])
+def test_attention_reads_packed_projections_in_place(causal):
+    """Q, K and V as sections of one packed [tokens, 3, heads, D] projection output and a token-major output
+    buffer, all passed as views: the same bits as the contiguous call, and nothing outside the buffer written."""
+    torch.manual_seed(11)
+    dev = torch.device("cuda", 0)
+    B, S, H, D = 2, 640, 3, 128
+    qkv = (torch.randn(B * S, 3 * H * D, device=dev) * 0.5).half()
+    v5 = qkv.view(B, S, 3, H, D)
+    q, k, v = (v5[:, :, i].permute(0, 2, 1, 3) for i in range(3))
+    assert not q.is_contiguous()
+    ref = w.flash_attention(q.contiguous(), k.contiguous(), v.contiguous(), causal)
+    buf = torch.zeros(B * S * H * D + 16, dtype=torch.float16, device=dev)
+    o = buf[8:8 + B * S * H * D].view(B, S, H, D)
+    got = w.flash_attention(q, k, v, causal, out=o.permute(0, 2, 1, 3))
+    w.check_status()
+    assert got.data_ptr() == o.data_ptr()
+    assert torch.equal(o.permute(0, 2, 1, 3), ref)
+    assert torch.all(buf[:8] == 0) and torch.all(buf[8 + B * S * H * D:] == 0)

@@ -60,6 +60,8 @@ SIGNATURES = {
     "wmma_ops_w4a16_token_block": (_c_int, [_c_int]),
     "wmma_ops_fmha_fwd": (_c_int, [_vp, _vp, _vp, _vp, _c_int, _c_int, _c_int, _c_int, _c_float, _c_int,
                                    _vp, _vp]),
+    "wmma_ops_fmha_fwd_strided": (_c_int, [_vp, _vp, _vp, _vp, _c_int, _c_int, _c_int, _c_int, ctypes.POINTER(ctypes.c_longlong),
+                                           _c_float, _c_int, _vp, _vp]),
     "wmma_ops_fmha_decode_workspace_bytes": (_c_size_t, [_c_int, _c_int, _c_int, _c_int, _c_int]),
     "wmma_ops_fmha_decode": (_c_int, [_vp, _vp, _vp, _vp, _c_int, _c_int, _c_int, _c_int, _c_int, _c_float, _c_int, _vp,
                                       _c_size_t, _vp, _vp]),

@@ -40,6 +40,7 @@ struct FaCfg {
 
 struct FaParams {
     __half* O;
+    long long o_row, o_head, o_batch;  // element strides of O between tokens, heads and sequences
     int B, H, S, D;
     float scale_log2;  // scale * log2(e)
     int causal;
@@ -107,6 +108,7 @@ fmha_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
     const int q_tiles = gridDim.x;
     const int q_tile = p.causal ? (q_tiles - 1 - static_cast<int>(blockIdx.x)) : static_cast<int>(blockIdx.x);
     const int bh = blockIdx.y;
+    const int b_idx = bh / p.H, h_idx = bh - b_idx * p.H;  // the tensor maps are (D, token, head, sequence)
     const int q0 = q_tile * FA_BM;
     const int kv_tiles_all = (p.S + FA_BN - 1) / FA_BN;
     const int n_tiles = p.causal ? min(kv_tiles_all, (q0 + FA_BM - 1) / FA_BN + 1) : kv_tiles_all;
@@ -146,7 +148,7 @@ fmha_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
             mbar_arrive_expect_tx(q_full, Cfg::Q_TILE_BYTES);
 #pragma unroll
             for (int b = 0; b < Cfg::DB; ++b)
-                tma_load_3d(q_smem + b * Cfg::Q_BOX_BYTES, &tmap_q, q_full, b * 64, q0, bh);
+                tma_load_4d(q_smem + b * Cfg::Q_BOX_BYTES, &tmap_q, q_full, b * 64, q0, h_idx, b_idx);
             for (int i = 0; i < n_tiles; ++i) {
                 const int s = i & 1;
                 const uint32_t ph = (i >> 1) & 1;
@@ -157,7 +159,7 @@ fmha_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
                 mbar_arrive_expect_tx(k_full(s), Cfg::KV_TILE_BYTES);
 #pragma unroll
                 for (int b = 0; b < Cfg::DB; ++b)
-                    tma_load_3d(k_smem(s) + b * Cfg::KV_BOX_BYTES, &tmap_k, k_full(s), b * 64, i * FA_BN, bh);
+                    tma_load_4d(k_smem(s) + b * Cfg::KV_BOX_BYTES, &tmap_k, k_full(s), b * 64, i * FA_BN, h_idx, b_idx);
                 if (!mbar_wait(v_empty(s), ph ^ 1u)) {
                     fa_report(p.status, 0, -i - 1);
                     break;
@@ -165,7 +167,7 @@ fmha_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
                 mbar_arrive_expect_tx(v_full(s), Cfg::KV_TILE_BYTES);
 #pragma unroll
                 for (int b = 0; b < Cfg::DB; ++b)
-                    tma_load_3d(v_smem(s) + b * Cfg::KV_BOX_BYTES, &tmap_v, v_full(s), b * 64, i * FA_BN, bh);
+                    tma_load_4d(v_smem(s) + b * Cfg::KV_BOX_BYTES, &tmap_v, v_full(s), b * 64, i * FA_BN, h_idx, b_idx);
             }
         }
     } else if (warp == 1) {
@@ -341,7 +343,7 @@ fmha_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
             tc_fence_after_sync();
             const float inv = (l_run > 0.f) ? 1.f / l_run : 0.f;
             const uint32_t o_addr = tmem_base + Cfg::O_COL + lane_addr;
-            __half* out = p.O + (static_cast<size_t>(bh) * p.S + q) * D;
+            __half* out = p.O + b_idx * p.o_batch + h_idx * p.o_head + static_cast<long long>(q) * p.o_row;
 #pragma unroll 1
             for (int c = 0; c < D / 32; ++c) {
                 uint32_t v[32];
@@ -370,8 +372,10 @@ fmha_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
     }
 }
 
+// st: element strides {row, head, batch} of Q, K and V (the last dimension, D, is contiguous)
 template <int D, int BN>
-static int launch_fmha(const void* Q, const void* K, const void* V, const FaParams& p, cudaStream_t stream) {
+static int launch_fmha(const void* Q, const void* K, const void* V, const long long* st, const FaParams& p,
+                       cudaStream_t stream) {
     using Cfg = FaCfg<D, BN>;
     static std::atomic<bool> attr_set[64];  // per device; setting the attribute twice is harmless
     int dev = 0;
@@ -382,17 +386,20 @@ static int launch_fmha(const void* Q, const void* K, const void* V, const FaPara
         attr_set[dev].store(true, std::memory_order_release);
     }
     CUtensorMap tq, tk, tv;
-    const uint64_t dims[3] = {static_cast<uint64_t>(D), static_cast<uint64_t>(p.S),
-                              static_cast<uint64_t>(p.B) * p.H};
-    const uint64_t strides[3] = {0, static_cast<uint64_t>(D) * 2, static_cast<uint64_t>(p.S) * D * 2};
-    const uint32_t box_q[3] = {64, FA_BM, 1};
-    const uint32_t box_kv[3] = {64, BN, 1};
-    int rc = encode_tmap(&tq, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 3, Q, dims, strides, box_q, CU_TENSOR_MAP_SWIZZLE_128B);
-    if (rc != WMMA_OPS_OK) return rc;
-    rc = encode_tmap(&tk, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 3, K, dims, strides, box_kv, CU_TENSOR_MAP_SWIZZLE_128B);
-    if (rc != WMMA_OPS_OK) return rc;
-    rc = encode_tmap(&tv, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 3, V, dims, strides, box_kv, CU_TENSOR_MAP_SWIZZLE_128B);
-    if (rc != WMMA_OPS_OK) return rc;
+    // (D, token, head, sequence): rows past the end of a sequence read as zeros whatever the layout
+    const uint64_t dims[4] = {static_cast<uint64_t>(D), static_cast<uint64_t>(p.S), static_cast<uint64_t>(p.H),
+                              static_cast<uint64_t>(p.B)};
+    const uint32_t box_q[4] = {64, FA_BM, 1, 1};
+    const uint32_t box_kv[4] = {64, BN, 1, 1};
+    const void* base[3] = {Q, K, V};
+    CUtensorMap* maps[3] = {&tq, &tk, &tv};
+    for (int i = 0; i < 3; ++i) {
+        const uint64_t strides[4] = {0, static_cast<uint64_t>(st[3 * i]) * 2, static_cast<uint64_t>(st[3 * i + 1]) * 2,
+                                     static_cast<uint64_t>(st[3 * i + 2]) * 2};
+        const int rc = encode_tmap(maps[i], CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 4, base[i], dims, strides,
+                                   i == 0 ? box_q : box_kv, CU_TENSOR_MAP_SWIZZLE_128B);
+        if (rc != WMMA_OPS_OK) return rc;
+    }
     dim3 grid((p.S + FA_BM - 1) / FA_BM, p.B * p.H);
     fmha_fwd_kernel<D, BN><<<grid, FA_THREADS, Cfg::SMEM_BYTES, stream>>>(tq, tk, tv, p);
     WB_CHECK_CUDA(cudaGetLastError());
@@ -401,21 +408,29 @@ static int launch_fmha(const void* Q, const void* K, const void* V, const FaPara
 
 }  // namespace wb
 
-extern "C" int wmma_ops_fmha_fwd(const void* Q, const void* K, const void* V, void* O, int B, int H, int S,
-                                 int D, float scale, int causal, int* status, void* stream) {
+extern "C" int wmma_ops_fmha_fwd_strided(const void* Q, const void* K, const void* V, void* O, int B, int H, int S,
+                                         int D, const long long* strides, float scale, int causal, int* status,
+                                         void* stream) {
     using namespace wb;
     WB_REQUIRE(B >= 0 && H >= 0 && S >= 0, WMMA_OPS_ERR_INVALID, "flash_attention: negative dimension");
     WB_REQUIRE(D == 64 || D == 128, WMMA_OPS_ERR_INVALID, "flash_attention: head dimension must be 64 or 128 (got %d)", D);
     if (B == 0 || H == 0 || S == 0) return WMMA_OPS_OK;
-    WB_REQUIRE(Q != nullptr && K != nullptr && V != nullptr && O != nullptr, WMMA_OPS_ERR_INVALID,
+    WB_REQUIRE(Q != nullptr && K != nullptr && V != nullptr && O != nullptr && strides != nullptr, WMMA_OPS_ERR_INVALID,
                "flash_attention: null pointer");
     WB_REQUIRE(static_cast<long long>(B) * H <= 65535, WMMA_OPS_ERR_INVALID,
                "flash_attention: B*H must not exceed 65535 (got %lld)", static_cast<long long>(B) * H);
     for (const void* ptr : {Q, K, V, static_cast<const void*>(O)})
         WB_REQUIRE(reinterpret_cast<uintptr_t>(ptr) % 16 == 0, WMMA_OPS_ERR_INVALID,
                    "flash_attention: tensors must be 16-byte aligned");
+    for (int i = 0; i < 12; ++i)
+        WB_REQUIRE(strides[i] >= (i % 3 == 0 ? D : 1) && strides[i] % 8 == 0, WMMA_OPS_ERR_INVALID,
+                   "flash_attention: strides must be multiples of 8 elements and rows at least D apart (stride %d is %lld)", i,
+                   strides[i]);
     FaParams p;
     p.O = static_cast<__half*>(O);
+    p.o_row = strides[9];
+    p.o_head = strides[10];
+    p.o_batch = strides[11];
     p.B = B;
     p.H = H;
     p.S = S;
@@ -425,6 +440,14 @@ extern "C" int wmma_ops_fmha_fwd(const void* Q, const void* K, const void* V, vo
     p.causal = causal ? 1 : 0;
     p.status = status;
     // 64-key tiles: two CTAs per SM (measured 850 vs 778 TFLOP/s with 128-key tiles at S = 4096)
-    if (D == 128) return launch_fmha<128, 64>(Q, K, V, p, static_cast<cudaStream_t>(stream));
-    return launch_fmha<64, 64>(Q, K, V, p, static_cast<cudaStream_t>(stream));
+    if (D == 128) return launch_fmha<128, 64>(Q, K, V, strides, p, static_cast<cudaStream_t>(stream));
+    return launch_fmha<64, 64>(Q, K, V, strides, p, static_cast<cudaStream_t>(stream));
+}
+
+extern "C" int wmma_ops_fmha_fwd(const void* Q, const void* K, const void* V, void* O, int B, int H, int S,
+                                 int D, float scale, int causal, int* status, void* stream) {
+    // contiguous [B, H, S, D]
+    const long long row = D, head = static_cast<long long>(S) * D, batch = static_cast<long long>(H) * S * D;
+    const long long strides[12] = {row, head, batch, row, head, batch, row, head, batch, row, head, batch};
+    return wmma_ops_fmha_fwd_strided(Q, K, V, O, B, H, S, D, strides, scale, causal, status, stream);
 }

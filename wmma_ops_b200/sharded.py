@@ -196,8 +196,16 @@ class ShardedDecoderLinears:
         if T % seq_len != 0 or heads * self.head_dim != self.q_cols:
             raise ValueError(f"{T} tokens are not whole sequences of {seq_len}, or the shard does not hold whole heads")
         batch = T // seq_len
-        # [T, 3, heads, D] -> [3, batch, heads, seq, D]: the layout flash_attention takes
-        qkv = qkv16.view(batch, seq_len, 3, heads, self.head_dim).permute(2, 0, 3, 1, 4).contiguous()
+        qkv = qkv16.view(batch, seq_len, 3, heads, self.head_dim)
+        if self._attention_fn is None:
+            # the library's kernel reads the Q, K and V sections of the projection output where they lie and
+            # writes token-major, which is what the O projection reads: no copies either side
+            o = torch.empty((batch, seq_len, heads, self.head_dim), dtype=torch.float16, device=qkv16.device)
+            q, k, v = (qkv[:, :, i].permute(0, 2, 1, 3) for i in range(3))
+            fn(q, k, v, causal, out=o.permute(0, 2, 1, 3))
+            return o.view(T, self.q_cols)
+        # a caller's attention function: [3, batch, heads, seq, D] contiguous in, [batch, heads, seq, D] out
+        qkv = qkv.permute(2, 0, 3, 1, 4).contiguous()
         o = fn(qkv[0], qkv[1], qkv[2], causal)
         return o.permute(0, 2, 1, 3).reshape(T, self.q_cols)     # a copy: [batch, seq, heads, D] row-major
 
