@@ -513,7 +513,23 @@ def measure_layer(w, dev, rank, world, steps):
                 layer = sharded.ShardedDecoderLinears(local, world=world, reduce_dtype=torch.float16, switch=sw,
                                                       attention=(seq_len, True))
                 record("nvswitch_fp16_partials_cuda_graph", *graphed(layer))
-                del layer, sw
+                del layer
+                # the fastest form of the linears-only layer: two token chunks (whole sequences each) on two
+                # streams, each sum following its GEMM
+                try:
+                    sw.max_ctas = 64
+                    w.set_sm_margin(16)
+                    layer = sharded.ShardedDecoderLinears(local, world=world, reduce_dtype=torch.float16, switch=sw,
+                                                          attention=(seq_len, True), chunks=2, follow=True)
+                    record("nvswitch_fp16_partials_2chunks_following_16sms_for_the_sum_cuda_graph", *graphed(layer))
+                    del layer
+                except Exception as e:
+                    with_attention["nvswitch_fp16_partials_2chunks_following_16sms_for_the_sum_cuda_graph"] = {
+                        "error": f"{type(e).__name__}: {str(e)[:200]}"}
+                finally:
+                    sw.max_ctas = 0
+                    w.set_sm_margin(0)
+                del sw
             except Exception as e:
                 with_attention["nvswitch_fp16_partials_cuda_graph"] = {"error": f"{type(e).__name__}: {str(e)[:200]}"}
             layer = sharded.ShardedDecoderLinears(local, world=world, reduce_dtype=torch.float32, attention=(seq_len, True))
