@@ -444,8 +444,10 @@ def measure_layer(w, dev, rank, world, steps):
                     # "following": each sum runs beside the GEMM that produces its input, token block by token block
                     (1, 0, 128, True, "_following_128ctas"), (2, 0, 64, True, "_following"),
                     (2, 0, 128, True, "_following_128ctas"), (4, 0, 128, True, "_following_128ctas"),
-                    (2, 16, 64, True, "_following_16sms_for_the_sum")):
-                if part == torch.float32 and (chunks != 2 or ctas != 64):
+                    (2, 16, 64, True, "_following_16sms_for_the_sum"),
+                    (2, 16, 80, True, "_following_80ctas_16sms_for_the_sum"),
+                    (2, 24, 96, True, "_following_96ctas_24sms_for_the_sum")):
+                if part == torch.float32 and (chunks != 2 or ctas != 64 or margin > 16):
                     continue        # the fp32-partials form is slower throughout: its main variants only
                 name = f"{label}_{chunks}chunks{suffix}_cuda_graph"
                 try:
