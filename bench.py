@@ -445,7 +445,6 @@ def measure_layer(w, dev, rank, world, steps):
                     (1, 0, 128, True, "_following_128ctas"), (2, 0, 64, True, "_following"),
                     (2, 0, 128, True, "_following_128ctas"), (4, 0, 128, True, "_following_128ctas"),
                     (2, 16, 64, True, "_following_16sms_for_the_sum"),
-                    (2, 16, 48, True, "_following_48ctas_16sms_for_the_sum"),
                     (2, 8, 32, True, "_following_32ctas_8sms_for_the_sum")):
                 if part == torch.float32 and (chunks != 2 or ctas != 64):
                     continue        # the fp32-partials form is slower throughout: its main variants only
